@@ -1,0 +1,266 @@
+"""ctypes binding of libdm_b200.so (the C ABI declared in include/dm_b200.h) and thin tensor-level wrappers.
+
+The library is the only compute path: if it is missing or fails to load, every call raises (there is no fallback).
+Wrappers allocate outputs with torch (the caching allocator, the tensors' device) and pass raw pointers plus the
+current CUDA stream of that device; a non-zero return code becomes a RuntimeError carrying the library's message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_LIB_PATH = None
+
+E4M3 = torch.float8_e4m3fn
+
+
+class DmShape(C.Structure):
+    _fields_ = [("B", C.c_int32), ("H", C.c_int32), ("Hk", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("causal", C.c_int32)]
+
+
+class DmStrides(C.Structure):
+    _fields_ = [("b", C.c_int64), ("n", C.c_int64), ("h", C.c_int64)]
+
+
+_ERR = (C.c_char_p, C.c_size_t)
+_P = C.c_void_p
+_SIGNATURES = {
+    "dm_build_info": (C.c_char_p, []),
+    "dm_kmean_scratch_bytes": (C.c_size_t, [C.c_int32] * 4),
+    "dm_kmean": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
+    "dm_quant": (C.c_int, [C.c_int32, _P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, *_ERR]),
+    "dm_quant_do": (C.c_int, [_P, DmStrides, _P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, *_ERR]),
+    "dm_fwd_fp8": (C.c_int, [_P] * 6 + [DmShape, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
+    "dm_delta_fp8": (C.c_int, [_P] * 9 + [DmShape, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_bwd_workspace_bytes": (C.c_int, [DmShape, C.c_int32, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "dm_bwd_fp8_pass1": (C.c_int, [_P] * 10 + [DmShape, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, *_ERR]),
+    "dm_bwd_fp8_pass2": (C.c_int, [_P] * 3 + [DmShape, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_gqa_fold": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_bwd_dbg_rowsum": (C.c_int, [_P] * 10 + [DmShape, _P, _P, _P, *_ERR]),
+    "dm_probe_mma": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
+    "dm_device_status": (C.c_int, [C.POINTER(C.c_int32), *_ERR]),
+}
+EXPORTS = tuple(_SIGNATURES)
+
+
+def library_path() -> str:
+    """The shared library this package loads: DM_SO if set, else the in-tree libdm_b200.so."""
+    so = os.environ.get("DM_SO")
+    if so:
+        if not os.path.isfile(so):
+            raise RuntimeError(f"DM_SO={so!r} does not exist")
+        return so
+    so = os.path.join(_HERE, "libdm_b200.so")
+    if not os.path.isfile(so):
+        raise RuntimeError("delta_matching_b200: libdm_b200.so is not built; run `python -m delta_matching_b200.build` "
+                           "in the checkout, or point DM_SO at a built library")
+    return so
+
+
+def lib():
+    """Load the library on first use and bind the signatures; missing symbols are an error."""
+    global _LIB, _LIB_PATH
+    if _LIB is None:
+        path = library_path()
+        handle = C.CDLL(path)
+        for name, (res, args) in _SIGNATURES.items():
+            try:
+                fn = getattr(handle, name)
+            except AttributeError as e:
+                raise RuntimeError(f"delta_matching_b200: {path} does not export {name}; rebuild the library") from e
+            fn.restype = res
+            fn.argtypes = args
+        _LIB, _LIB_PATH = handle, path
+    return _LIB
+
+
+def loaded_library():
+    return _LIB_PATH
+
+
+def build_info() -> str:
+    return lib().dm_build_info().decode()
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _call(name, *args):
+    err = C.create_string_buffer(512)
+    rc = getattr(lib(), name)(*args, err, len(err))
+    if rc != 0:
+        raise RuntimeError(f"delta_matching_b200.{name}: {err.value.decode(errors='replace')} (code {rc})")
+
+
+def _strides_bnhd(t):
+    """Element strides (batch, seqlen, head) of a (B, N, H, D) view with unit head_dim stride."""
+    return DmStrides(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _shape(B, H, Hk, N, D, causal):
+    return DmShape(B, H, Hk, N, D, 1 if causal else 0)
+
+
+def blocks(D: int):
+    """Rows per Q / dO scale and keys per K / V scale: (64, 32) at head_dim 256, (128, 64) at head_dim 128."""
+    return (64, 32) if D >= 256 else (128, 64)
+
+
+def _unit_lane(t):
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# tensor-level wrappers; all take flash-layout (B, N, heads, D) bf16 views and code tensors [B*heads, N, D]
+# ----------------------------------------------------------------------------------------------------------------------
+def kmean(k_bnhd):
+    B, N, Hk, D = k_bnhd.shape
+    k_bnhd = _unit_lane(k_bnhd)
+    with torch.cuda.device(k_bnhd.device):
+        km = torch.empty(B * Hk, D, device=k_bnhd.device, dtype=torch.float32)
+        scratch = torch.empty(lib().dm_kmean_scratch_bytes(B, Hk, N, D) // 4, device=k_bnhd.device, dtype=torch.float32)
+        _call("dm_kmean", _ptr(k_bnhd), _strides_bnhd(k_bnhd), B, Hk, N, D, _ptr(km), _ptr(scratch), _stream(k_bnhd.device))
+    return km
+
+
+def quant(mode, x_bnhd, km=None):
+    """mode 0 = Q, 1 = K (needs km), 2 = V.  Returns (codes [B*heads, N, D] e4m3, scales [B*heads, N/blk] fp32)."""
+    B, N, Hh, D = x_bnhd.shape
+    x_bnhd = _unit_lane(x_bnhd)
+    blk = blocks(D)[0 if mode == 0 else 1]
+    with torch.cuda.device(x_bnhd.device):
+        codes = torch.empty(B * Hh, N, D, device=x_bnhd.device, dtype=E4M3)
+        scales = torch.empty(B * Hh, max(N // blk, 1), device=x_bnhd.device, dtype=torch.float32)
+        _call("dm_quant", mode, _ptr(x_bnhd), _strides_bnhd(x_bnhd), B, Hh, N, D, _ptr(km), _ptr(codes), _ptr(scales),
+              _stream(x_bnhd.device))
+    return codes, scales
+
+
+def quant_do(dO_bnhd, o_bnhd=None):
+    """dO codes / scales and, when o is given, the stale delta [B*H, N] fp32."""
+    B, N, H, D = dO_bnhd.shape
+    dO_bnhd = _unit_lane(dO_bnhd)
+    with torch.cuda.device(dO_bnhd.device):
+        codes = torch.empty(B * H, N, D, device=dO_bnhd.device, dtype=E4M3)
+        scales = torch.empty(B * H, max(N // blocks(D)[0], 1), device=dO_bnhd.device, dtype=torch.float32)
+        delta = None
+        os_ = DmStrides(0, 0, 0)
+        if o_bnhd is not None:
+            o_bnhd = _unit_lane(o_bnhd)
+            delta = torch.empty(B * H, N, device=dO_bnhd.device, dtype=torch.float32)
+            os_ = _strides_bnhd(o_bnhd)
+        _call("dm_quant_do", _ptr(dO_bnhd), _strides_bnhd(dO_bnhd), _ptr(o_bnhd), os_, B, H, N, D, _ptr(codes), _ptr(scales),
+              _ptr(delta), _stream(dO_bnhd.device))
+    return codes, scales, delta
+
+
+def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=None):
+    """O (B, N, H, D) bf16 and LSE [B*H, N] fp32; with a head range only those heads are written."""
+    BH, N, D = Q8.shape
+    hcount = H if hcount is None else hcount
+    dev = Q8.device
+    with torch.cuda.device(dev):
+        if out is None:
+            o = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
+            lse = torch.empty(B * H, N, device=dev, dtype=torch.float32)
+        else:
+            o, lse = out
+        _call("dm_fwd_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _shape(B, H, Hk, N, D, causal), h0,
+              hcount, _ptr(o), _ptr(lse), _stream(dev))
+    return o, lse
+
+
+def delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, h0=0, hcount=None, out=None):
+    BH, N, D = Q8.shape
+    hcount = H if hcount is None else hcount
+    dev = Q8.device
+    with torch.cuda.device(dev):
+        delta = torch.empty(B * H, N, device=dev, dtype=torch.float32) if out is None else out
+        _call("dm_delta_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
+              _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(delta), _stream(dev))
+    return delta
+
+
+def bwd_workspace_bytes(B, H, Hk, N, D, causal, hcount):
+    a, b = C.c_size_t(0), C.c_size_t(0)
+    rc = lib().dm_bwd_workspace_bytes(_shape(B, H, Hk, N, D, causal), hcount, C.byref(a), C.byref(b))
+    if rc != 0:
+        raise RuntimeError(f"delta_matching_b200.dm_bwd_workspace_bytes failed (code {rc})")
+    return a.value, b.value
+
+
+def bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, h0=0, hcount=None, out=None, ws=None):
+    """dK, dV (B, N, H, D) bf16 per query head plus the dS' / psi workspace for pass 2."""
+    BH, N, D = Q8.shape
+    hcount = H if hcount is None else hcount
+    dev = Q8.device
+    with torch.cuda.device(dev):
+        if out is None:
+            dk = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
+            dv = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
+        else:
+            dk, dv = out
+        if ws is None:
+            nb_ds, nb_psi = bwd_workspace_bytes(B, H, Hk, N, D, causal, hcount)
+            ws = (torch.empty(nb_ds, device=dev, dtype=torch.uint8), torch.empty(nb_psi // 4, device=dev, dtype=torch.float32))
+        _call("dm_bwd_fp8_pass1", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
+              _ptr(delta), _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(dk), _ptr(dv), _ptr(ws[0]), _ptr(ws[1]), _stream(dev))
+    return dk, dv, ws
+
+
+def bwd_pass2(ws, K8, B, H, Hk, N, D, causal, h0=0, hcount=None, out=None):
+    hcount = H if hcount is None else hcount
+    dev = K8.device
+    with torch.cuda.device(dev):
+        dq = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16) if out is None else out
+        _call("dm_bwd_fp8_pass2", _ptr(ws[0]), _ptr(ws[1]), _ptr(K8), _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(dq),
+              _stream(dev))
+    return dq
+
+
+def gqa_fold(x_bnhd, Hk):
+    B, N, H, D = x_bnhd.shape
+    if H == Hk:
+        return x_bnhd
+    x_bnhd = x_bnhd.contiguous()
+    with torch.cuda.device(x_bnhd.device):
+        out = torch.empty(B, N, Hk, D, device=x_bnhd.device, dtype=torch.bfloat16)
+        _call("dm_gqa_fold", _ptr(x_bnhd), B, N, H, Hk, D, _ptr(out), _stream(x_bnhd.device))
+    return out
+
+
+def bwd_dbg_rowsum(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal):
+    BH, N, D = Q8.shape
+    dev = Q8.device
+    with torch.cuda.device(dev):
+        rows = torch.empty(B * H, N, device=dev, dtype=torch.float32)
+        rabs = torch.empty(B * H, N, device=dev, dtype=torch.float32)
+        _call("dm_bwd_dbg_rowsum", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
+              _ptr(delta), _shape(B, H, Hk, N, D, causal), _ptr(rows), _ptr(rabs), _stream(dev))
+    return rows, rabs
+
+
+def probe_mma(a_tile, b_tile, a_mn, b_mn, n_cols=128, via_st=False):
+    dev = a_tile.device
+    with torch.cuda.device(dev):
+        c = torch.empty(128, n_cols, device=dev, dtype=torch.float32)
+        echo = torch.zeros(128, 128, device=dev, dtype=torch.uint8)
+        _call("dm_probe_mma", _ptr(a_tile), _ptr(b_tile), int(a_mn), int(b_mn), n_cols, int(via_st), _ptr(c), _ptr(echo), _stream(dev))
+    return c, echo
+
+
+def device_status(device=None) -> int:
+    """Synchronise the device and read-and-clear the status word the kernels' bounded waits write (0 = clean)."""
+    v = C.c_int32(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _call("dm_device_status", C.byref(v))
+    return v.value

@@ -1,0 +1,302 @@
+// Producers: per-head K mean, block quantizers bf16 -> e4m3 codes + fp32 scales for Q, K, V, dO (with the optional
+// stale delta), and the GQA fold of per-query-head gradients.  All HBM-bound: one warp owns one row (256 or 512
+// contiguous bytes), loads are 8/16 bytes per lane, code stores 4/8 bytes per lane, block amax by warp shuffles.
+//
+// Bit-exactness contract (checked against the CPU oracle, which is pinned to the reference's Triton kernels):
+//   * every arithmetic step is an explicitly rounded IEEE operation (__fmul_rn, __fsub_rn, __fdiv_rn, __fadd_rn), so
+//     the compiler cannot contract or reassociate; this file must never be built with --use_fast_math;
+//   * Q / K / V scale = max(amax, 1e-30) / 448 (division), dO scale = max(amax, 1e-30) * fp32(1/448) (multiplication);
+//   * codes = cvt.rn.satfinite.e4m3(clamp(x / scale, +-448)) with an IEEE division;
+//   * K mean = (((0 + s_0) + s_1) + ...) / N with s_j the sum of the 64 rows of chunk j in ascending row order.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "dm_host.h"
+
+namespace {
+
+constexpr float kE4M3Max = 448.0f;
+constexpr float kTiny = 1e-30f;
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
+
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+// ---- K mean ---------------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256) kmean_partial_kernel(const __nv_bfloat16* __restrict__ k, int64_t sb, int64_t sn, int64_t sh,
+                                                            int Hk, int N, float* __restrict__ partials) {
+    constexpr int TPC = D / 2;            // threads per 64-row chunk (two columns each)
+    constexpr int CPB = 256 / TPC;        // chunks per block
+    const int bh = blockIdx.y, b = bh / Hk, h = bh % Hk;
+    const int chunk = blockIdx.x * CPB + threadIdx.x / TPC;
+    const int c2 = threadIdx.x % TPC;
+    const __nv_bfloat16* base = k + b * sb + h * sh + (int64_t)chunk * 64 * sn + 2 * c2;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll 16
+    for (int r = 0; r < 64; ++r) {
+        uint32_t u = *reinterpret_cast<const uint32_t*>(base + (int64_t)r * sn);
+        s0 = __fadd_rn(s0, bf16_lo(u));
+        s1 = __fadd_rn(s1, bf16_hi(u));
+    }
+    float2* out = reinterpret_cast<float2*>(partials + ((int64_t)bh * (N / 64) + chunk) * D) + c2;
+    *out = make_float2(s0, s1);
+}
+
+template <int D>
+__global__ void kmean_fold_kernel(const float* __restrict__ partials, int N, float* __restrict__ km) {
+    const int bh = blockIdx.x, d = threadIdx.x;
+    const float* p = partials + (int64_t)bh * (N / 64) * D + d;
+    float acc = 0.f;
+    for (int j = 0; j < N / 64; ++j) acc = __fadd_rn(acc, p[(int64_t)j * D]);
+    km[(int64_t)bh * D + d] = __fdiv_rn(acc, (float)N);
+}
+
+// ---- block quantizer ------------------------------------------------------------------------------------------------
+// MODE 0 = Q, 1 = K, 2 = V, 3 = dO.
+template <int D, int MODE>
+__global__ void __launch_bounds__(256) quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sn, int64_t sh,
+                                                    const __nv_bfloat16* __restrict__ o, int64_t ob, int64_t on, int64_t oh,
+                                                    const float* __restrict__ km, uint8_t* __restrict__ codes,
+                                                    float* __restrict__ scales, float* __restrict__ delta, int heads, int N, float sm) {
+    constexpr int BLK = (MODE == 0 || MODE == 3) ? (D == 128 ? 128 : 64) : (D == 128 ? 64 : 32);
+    constexpr int E = D / 32;             // elements per lane
+    constexpr int RPW = BLK / 8;          // rows per warp
+    const int blk = blockIdx.x, bh = blockIdx.y, b = bh / heads, h = bh % heads;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __shared__ float s_amax[8];
+
+    float kmv[E];
+    if (MODE == 1) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) kmv[e] = km[(int64_t)bh * D + l * E + e];
+    }
+    float v[RPW][E];
+    float amax = 0.f;
+    const __nv_bfloat16* xbase = x + b * sb + h * sh + l * E;
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        const int row = blk * BLK + r * 8 + w;
+        const __nv_bfloat16* p = xbase + (int64_t)row * sn;
+        uint32_t u[E / 2];
+        if (E == 4) {
+            uint2 t = *reinterpret_cast<const uint2*>(p);
+            u[0] = t.x; u[1] = t.y;
+        } else {
+            uint4 t = *reinterpret_cast<const uint4*>(p);
+            u[0] = t.x; u[1] = t.y; u[E / 2 - 2] = t.z; u[E / 2 - 1] = t.w;
+        }
+#pragma unroll
+        for (int e = 0; e < E / 2; ++e) {
+            v[r][2 * e] = bf16_lo(u[e]);
+            v[r][2 * e + 1] = bf16_hi(u[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            if (MODE == 0) v[r][e] = __fmul_rn(v[r][e], sm);
+            if (MODE == 1) v[r][e] = __fsub_rn(v[r][e], kmv[e]);
+            amax = fmaxf(amax, fabsf(v[r][e]));
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (l == 0) s_amax[w] = amax;
+    __syncthreads();
+    amax = s_amax[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_amax[i]);
+    const float base = fmaxf(amax, kTiny);
+    const float s = (MODE == 3) ? __fmul_rn(base, __fdiv_rn(1.0f, kE4M3Max)) : __fdiv_rn(base, kE4M3Max);
+    if (threadIdx.x == 0) scales[(int64_t)bh * (N / BLK) + blk] = s;
+
+    uint8_t* cbase = codes + ((int64_t)bh * N) * D + l * E;
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        const int row = blk * BLK + r * 8 + w;
+        float qv[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) qv[e] = fminf(fmaxf(__fdiv_rn(v[r][e], s), -kE4M3Max), kE4M3Max);
+        if (E == 4) {
+            *reinterpret_cast<uint32_t*>(cbase + (int64_t)row * D) = e4m3x4(qv[0], qv[1], qv[2], qv[3]);
+        } else {
+            uint2 t;
+            t.x = e4m3x4(qv[0], qv[1], qv[2], qv[3]);
+            t.y = e4m3x4(qv[E - 4], qv[E - 3], qv[E - 2], qv[E - 1]);
+            *reinterpret_cast<uint2*>(cbase + (int64_t)row * D) = t;
+        }
+        if (MODE == 3 && delta != nullptr) {
+            // stale delta from the RAW dO (v holds it unscaled in this mode) and the bf16 O
+            const __nv_bfloat16* po = o + b * ob + h * oh + (int64_t)row * on + l * E;
+            uint32_t u[E / 2];
+            if (E == 4) {
+                uint2 t = *reinterpret_cast<const uint2*>(po);
+                u[0] = t.x; u[1] = t.y;
+            } else {
+                uint4 t = *reinterpret_cast<const uint4*>(po);
+                u[0] = t.x; u[1] = t.y; u[E / 2 - 2] = t.z; u[E / 2 - 1] = t.w;
+            }
+            float acc = __fmul_rn(v[r][0], bf16_lo(u[0]));
+            acc = __fadd_rn(acc, __fmul_rn(v[r][1], bf16_hi(u[0])));
+#pragma unroll
+            for (int e = 1; e < E / 2; ++e) {
+                acc = __fadd_rn(acc, __fmul_rn(v[r][2 * e], bf16_lo(u[e])));
+                acc = __fadd_rn(acc, __fmul_rn(v[r][2 * e + 1], bf16_hi(u[e])));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+            if (l == 0) delta[(int64_t)bh * N + row] = acc;
+        }
+    }
+}
+
+// ---- GQA fold -------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gqa_fold_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int64_t total_vec, int H,
+                                                       int Hk, int D) {
+    const int vpr = D / 8;                                   // 16-byte vectors per head row
+    const int rep = H / Hk;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / vpr;                         // (b, n, hk)
+        const int c = (int)(i % vpr);
+        const int64_t bn = row / Hk;
+        const int hk = (int)(row % Hk);
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int r = 0; r < rep; ++r) {
+            uint4 t = x[((bn * H) + hk * rep + r) * vpr + c];
+            uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[2 * e] = (r == 0) ? bf16_lo(u[e]) : __fadd_rn(acc[2 * e], bf16_lo(u[e]));
+                acc[2 * e + 1] = (r == 0) ? bf16_hi(u[e]) : __fadd_rn(acc[2 * e + 1], bf16_hi(u[e]));
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+            o[e] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+int check_geometry(int B, int heads, int N, int D, char* err, size_t errlen) {
+    DM_REQUIRE(D == 128 || D == 256, DM_ERR_ARG, "head_dim must be 128 or 256 (got %d)", D);
+    const int mult = D == 128 ? 256 : 128;
+    DM_REQUIRE(N > 0 && N % mult == 0, DM_ERR_ARG, "seqlen must be a positive multiple of %d at head_dim %d (got %d)", mult, D, N);
+    DM_REQUIRE(B > 0 && heads > 0, DM_ERR_ARG, "empty batch or no heads");
+    DM_REQUIRE((int64_t)B * heads <= 65535, DM_ERR_ARG, "batch * nheads must be at most 65535 (got %lld)", (long long)B * heads);
+    return DM_OK;
+}
+
+int check_strides(const void* p, DmStrides s, int D, const char* name, char* err, size_t errlen) {
+    DM_REQUIRE((reinterpret_cast<uintptr_t>(p) & 15u) == 0, DM_ERR_ARG, "%s is not 16-byte aligned", name);
+    DM_REQUIRE(s.b % 8 == 0 && s.n % 8 == 0 && s.h % 8 == 0, DM_ERR_ARG,
+               "%s: batch / seqlen / head strides must be multiples of 8 elements (16-byte aligned rows)", name);
+    DM_REQUIRE(s.n >= D, DM_ERR_ARG, "%s: seqlen stride %lld is smaller than head_dim", name, (long long)s.n);
+    return DM_OK;
+}
+
+}  // namespace
+
+extern "C" size_t dm_kmean_scratch_bytes(int32_t B, int32_t Hk, int32_t N, int32_t D) {
+    if (B <= 0 || Hk <= 0 || N <= 0 || D <= 0) return 0;
+    return (size_t)B * Hk * (N / 64) * D * sizeof(float);
+}
+
+extern "C" int dm_kmean(const void* k, DmStrides ks, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, float* partials,
+                        void* stream, char* err, size_t errlen) {
+    int rc = check_geometry(B, Hk, N, D, err, errlen);
+    if (rc) return rc;
+    if ((rc = dmh::check_device_ptr(k, "k", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(km, "km", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(partials, "partials", err, errlen))) return rc;
+    if ((rc = check_strides(k, ks, D, "k", err, errlen))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(k);
+    if (D == 128) {
+        kmean_partial_kernel<128><<<dim3(N / 64 / 4, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
+        kmean_fold_kernel<128><<<B * Hk, 128, 0, st>>>(partials, N, km);
+    } else {
+        kmean_partial_kernel<256><<<dim3(N / 64 / 2, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
+        kmean_fold_kernel<256><<<B * Hk, 256, 0, st>>>(partials, N, km);
+    }
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+template <int D, int MODE>
+static void launch_quant(const void* x, DmStrides xs, const void* o, DmStrides os, const float* km, void* codes, float* scales,
+                         float* delta, int B, int heads, int N, cudaStream_t st) {
+    constexpr int BLK = (MODE == 0 || MODE == 3) ? (D == 128 ? 128 : 64) : (D == 128 ? 64 : 32);
+    const float sm = D == 128 ? 0.08838834764831845f : 0.0625f;
+    quant_kernel<D, MODE><<<dim3(N / BLK, B * heads), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), xs.b, xs.n, xs.h, static_cast<const __nv_bfloat16*>(o), os.b, os.n, os.h, km,
+        static_cast<uint8_t*>(codes), scales, delta, heads, N, sm);
+}
+
+extern "C" int dm_quant(int32_t mode, const void* x, DmStrides xs, int32_t B, int32_t heads, int32_t N, int32_t D, const float* km,
+                        void* codes, float* scales, void* stream, char* err, size_t errlen) {
+    DM_REQUIRE(mode >= 0 && mode <= 2, DM_ERR_ARG, "mode must be 0 (Q), 1 (K) or 2 (V); got %d", mode);
+    int rc = check_geometry(B, heads, N, D, err, errlen);
+    if (rc) return rc;
+    if ((rc = dmh::check_device_ptr(x, "x", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(codes, "codes", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(scales, "scales", err, errlen))) return rc;
+    if (mode == 1 && (rc = dmh::check_device_ptr(km, "km", err, errlen))) return rc;
+    if ((rc = check_strides(x, xs, D, "x", err, errlen))) return rc;
+    DM_REQUIRE(dmh::aligned16(codes), DM_ERR_ARG, "codes is not 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DmStrides z = {0, 0, 0};
+#define DM_Q(DD, MM) launch_quant<DD, MM>(x, xs, nullptr, z, km, codes, scales, nullptr, B, heads, N, st)
+    if (D == 128) { if (mode == 0) DM_Q(128, 0); else if (mode == 1) DM_Q(128, 1); else DM_Q(128, 2); }
+    else          { if (mode == 0) DM_Q(256, 0); else if (mode == 1) DM_Q(256, 1); else DM_Q(256, 2); }
+#undef DM_Q
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+extern "C" int dm_quant_do(const void* dO, DmStrides dos, const void* o, DmStrides os, int32_t B, int32_t H, int32_t N, int32_t D,
+                           void* codes, float* scales, float* delta, void* stream, char* err, size_t errlen) {
+    int rc = check_geometry(B, H, N, D, err, errlen);
+    if (rc) return rc;
+    if ((rc = dmh::check_device_ptr(dO, "dO", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(codes, "codes", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(scales, "scales", err, errlen))) return rc;
+    if ((rc = check_strides(dO, dos, D, "dO", err, errlen))) return rc;
+    DM_REQUIRE((o == nullptr) == (delta == nullptr), DM_ERR_ARG, "o and delta must be given together (stale delta) or both NULL");
+    if (delta) {
+        if ((rc = dmh::check_device_ptr(o, "o", err, errlen))) return rc;
+        if ((rc = dmh::check_device_ptr(delta, "delta", err, errlen))) return rc;
+        if ((rc = check_strides(o, os, D, "o", err, errlen))) return rc;
+    }
+    DM_REQUIRE(dmh::aligned16(codes), DM_ERR_ARG, "codes is not 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (D == 128) launch_quant<128, 3>(dO, dos, o, os, nullptr, codes, scales, delta, B, H, N, st);
+    else          launch_quant<256, 3>(dO, dos, o, os, nullptr, codes, scales, delta, B, H, N, st);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+extern "C" int dm_gqa_fold(const void* x, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, void* out, void* stream, char* err,
+                           size_t errlen) {
+    DM_REQUIRE(B > 0 && N > 0 && H > 0 && Hk > 0 && H % Hk == 0, DM_ERR_ARG, "nheads (%d) must be a positive multiple of nheads_k (%d)", H, Hk);
+    DM_REQUIRE(D % 8 == 0, DM_ERR_ARG, "head_dim must be a multiple of 8");
+    int rc;
+    if ((rc = dmh::check_device_ptr(x, "x", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(out, "out", err, errlen))) return rc;
+    DM_REQUIRE(dmh::aligned16(x) && dmh::aligned16(out), DM_ERR_ARG, "x / out must be 16-byte aligned");
+    const int64_t total = (int64_t)B * N * Hk * (D / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gqa_fold_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(x), static_cast<uint4*>(out), total, H, Hk, D);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}

@@ -1,0 +1,121 @@
+/* libdm_b200: C ABI of the B200 (sm_100a) Delta-Matching fp8 attention kernels.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns 0 or a negative DM_ERR_* code and, on
+ * error, writes a message into `err` (may be NULL).  Nothing here exits, aborts or traps.  The caller owns every
+ * buffer; all pointers are device pointers on the CURRENT device; `stream` is a cudaStream_t passed as void*.
+ * Work is enqueued on `stream` and the call returns without synchronising.
+ *
+ * Layouts.  bf16 tensors use the flash-attention layout (batch, seqlen, heads, head_dim) with explicit element strides
+ * for batch / seqlen / head (the head_dim stride must be 1).  fp8 code tensors are [batch*heads, seqlen, head_dim]
+ * e4m3, contiguous, 16-byte aligned; scales are contiguous fp32 [batch*heads, seqlen / rows_per_scale] with
+ * rows_per_scale = (128, 64) for (Q / dO, K / V) at head_dim 128 and (64, 32) at head_dim 256.  Query head h reads KV
+ * head h / (H / Hk).
+ *
+ * Each declaration cites the reference interface it replaces (paths inside the haok1402/delta-matching project).
+ */
+#ifndef DM_B200_H
+#define DM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    DM_OK = 0,
+    DM_ERR_ARG = -1,        /* bad shape / pointer / alignment / size; nothing was launched */
+    DM_ERR_CUDA = -2,       /* a CUDA runtime or driver call failed */
+    DM_ERR_UNSUPPORTED = -3,/* valid request this build does not implement (message says which) */
+    DM_ERR_DEVICE = -4      /* a kernel reported a bounded-wait timeout (see dm_device_status) */
+};
+
+/* Geometry of one attention problem. D in {128, 256}; N % 256 == 0 at D=128, N % 128 == 0 at D=256; H % Hk == 0. */
+typedef struct DmShape {
+    int32_t B, H, Hk, N, D;
+    int32_t causal; /* 0 / 1 */
+} DmShape;
+
+/* Element strides of a (batch, seqlen, heads, head_dim) bf16 tensor; the head_dim stride is 1. */
+typedef struct DmStrides {
+    int64_t b, n, h;
+} DmStrides;
+
+/* Library identity: version, numerics tag, build flags.  Replaces torch.ops.delta_matching.build_hd128 / build_gt /
+ * build_bf16dp (csrc/delta_matching_api.cpp:684-704) and feeds kernel_version() (delta_matching/__init__.py:65-89). */
+const char* dm_build_info(void);
+
+/* Per-head K mean over the sequence, fp32 [B*Hk, D], bit-exact fold order: 64-row chunk sums (rows ascending), chunks
+ * folded serially, one IEEE division by N.  `partials` is caller-provided scratch of dm_kmean_scratch_bytes() bytes.
+ * Replaces _kmean_kernel (delta_matching/quant.py:17-29) and kmean_m17 (delta_matching/producers.py:75-94). */
+size_t dm_kmean_scratch_bytes(int32_t B, int32_t Hk, int32_t N, int32_t D);
+int dm_kmean(const void* k_bf16, DmStrides ks, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, float* partials,
+             void* stream, char* err, size_t errlen);
+
+/* Block quantizers: bf16 -> e4m3 codes + per-block fp32 scales.
+ * mode 0 = Q (x * fp32(D^-0.5)), 1 = K (x - km[head, d]; `km` required), 2 = V (as is): scale = max(amax, 1e-30) / 448,
+ * code = e4m3_rtne(clamp(x / scale, +-448)) with IEEE division.
+ * Replaces _quant_kernel MODE 0/1/2 (delta_matching/quant.py:32-86) as launched by quant_q_m17 / quant_kv_m17
+ * (delta_matching/producers.py:149-204).  No transposed twins are produced: the sm_100a MMAs read both majors. */
+int dm_quant(int32_t mode, const void* x_bf16, DmStrides xs, int32_t B, int32_t heads, int32_t N, int32_t D, const float* km,
+             void* codes, float* scales, void* stream, char* err, size_t errlen);
+
+/* dO quantizer: scale = max(amax, 1e-30) * fp32(1/448) (a multiply), codes as above.  When `o_bf16` and `delta` are
+ * non-NULL also writes the stale delta[b*H + h, n] = sum_d float(dO) * float(O) from the raw bf16 values.
+ * Replaces _doq_m17_kernel / doq_m17 (delta_matching/producers.py:235-329) and _doq2_kernel (delta_matching/doq.py:12-70). */
+int dm_quant_do(const void* do_bf16, DmStrides dos, const void* o_bf16, DmStrides os, int32_t B, int32_t H, int32_t N, int32_t D,
+                void* codes, float* scales, float* delta, void* stream, char* err, size_t errlen);
+
+/* Forward: O (B, N, H, D) bf16 contiguous, LSE [B*H, N] fp32 (natural log of the sm-scaled, K-centred scores).
+ * h0 / hcount select a range of query heads (all batches); outputs are indexed by the full head number.
+ * Replaces torch.ops.delta_matching.fwd_fp8 (csrc/delta_matching_api.cpp:105-199). */
+int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
+               DmShape s, int32_t h0, int32_t hcount, void* o_bf16, float* lse, void* stream, char* err, size_t errlen);
+
+/* Pass 0: the matched delta [B*H, N] fp32 from the backward's own fp8 P-hat / dP pair.
+ * Replaces torch.ops.delta_matching.delta_fp8 (csrc/delta_matching_api.cpp:471-600). */
+int dm_delta_fp8(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                 const float* v8s, const float* do8s, const float* lse, DmShape s, int32_t h0, int32_t hcount, float* delta,
+                 void* stream, char* err, size_t errlen);
+
+/* Workspace of the backward for `hcount` query heads per batch: dS' code tiles (e4m3) and their psi scales (fp32).
+ * Replaces the allocations in bwd_fp8_core (csrc/delta_matching_api.cpp:288-306). */
+int dm_bwd_workspace_bytes(DmShape s, int32_t hcount, size_t* ds8_bytes, size_t* psi_bytes);
+
+/* Pass 1: dK, dV (B, N, H, D) bf16 per QUERY head, the dS' code tiles and psi.  Pass 2: dQ (B, N, H, D) bf16.
+ * Together they replace torch.ops.delta_matching.bwd_fp8_t (csrc/delta_matching_api.cpp:224-392, 429-438); the split
+ * lets a caller run pass 2 of one head group on another stream (delta_matching/split.py:51-92). */
+int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                     const float* v8s, const float* do8s, const float* lse, const float* delta, DmShape s, int32_t h0,
+                     int32_t hcount, void* dk_bf16, void* dv_bf16, void* ds8_ws, float* psi_ws, void* stream, char* err,
+                     size_t errlen);
+int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape s, int32_t h0, int32_t hcount,
+                     void* dq_bf16, void* stream, char* err, size_t errlen);
+
+/* GQA fold: per-query-head grads (B, N, H, D) bf16 -> (B, N, Hk, D) bf16, fp32 sum over the H/Hk heads of a KV head in
+ * ascending head order, one bf16 rounding.  Replaces dk.reshape(B, Hk, rep, N, D).sum(2) (delta_matching/attn.py:111-118). */
+int dm_gqa_fold(const void* x_bf16, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, void* out_bf16, void* stream,
+                char* err, size_t errlen);
+
+/* Debug: row sums and absolute row sums of P-hat * (dP - delta) / 256 over all visible keys, fp32 [B*H, N] each, from
+ * the same operands and arithmetic as pass 1.  Replaces the DM_DBG ops bwd_fp8_dbg / delta_fp8_dbg
+ * (csrc/delta_matching_api.cpp:612-680). */
+int dm_bwd_dbg_rowsum(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                      const float* v8s, const float* do8s, const float* lse, const float* delta, DmShape s, float* rows,
+                      float* rows_abs, void* stream, char* err, size_t errlen);
+
+/* Self-test of the tensor-core operand conventions: C[128, 128] fp32 = A * B on e4m3 tiles of 128 x 128 bytes.
+ * a_mn / b_mn = 0: the tile's rows are M (or N) and its 128 bytes are K; 1: its rows are K and its 128 bytes are M (or N).
+ * via_st = 1 also round-trips A through thread-written swizzled shared memory and stores it back with a TMA store into
+ * `a_echo` (128 x 128 bytes).  No counterpart in the reference (its wgmma path fixes the majors in CuTe types). */
+int dm_probe_mma(const void* a_tile, const void* b_tile, int32_t a_mn, int32_t b_mn, int32_t n_cols, int32_t via_st,
+                 float* c_out, void* a_echo, void* stream, char* err, size_t errlen);
+
+/* Reads (and clears) the current device's status word; synchronises the device.  0 = no kernel gave up a wait. */
+int dm_device_status(int32_t* status, char* err, size_t errlen);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DM_B200_H */

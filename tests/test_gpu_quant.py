@@ -1,0 +1,85 @@
+"""CUDA quantizers against the CPU oracle: k-mean, scales and codes bit-exact (the oracle is pinned to the reference's
+Triton kernels by tests/test_oracle.py), on the golden inputs, on strided packed-qkv views, at both head dims."""
+import numpy as np
+import pytest
+import torch
+
+from delta_matching_b200 import _lib
+from oracle import dm_oracle as O
+from make_quant_golden import golden_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _eq8(a, b):
+    return torch.equal(a.cpu().view(torch.uint8), b.view(torch.uint8))
+
+
+def _check_all(q, k, v, dO, Oo):
+    """q (B, N, H, D) etc. on the CPU (any strides); compares every producer output with the oracle bit for bit."""
+    Q8, Q8s = O.quant_q(q.transpose(1, 2))
+    K8, K8s, km = O.quant_k(k.transpose(1, 2))
+    V8, V8s = O.quant_v(v.transpose(1, 2))
+    dO8, dO8s = O.quant_do(dO)
+    dlt = O.stale_delta(dO, Oo)
+    qd, kd, vd, dod, od = (t.cuda() for t in (q, k, v, dO, Oo))
+    if q.stride() != q.contiguous().stride():      # keep the strided view on the device too
+        pass
+    gkm = _lib.kmean(kd)
+    assert torch.equal(gkm.cpu(), km), "k-mean differs"
+    for name, (gc, gs), (c, s) in (("q", _lib.quant(0, qd), (Q8, Q8s)), ("k", _lib.quant(1, kd, gkm), (K8, K8s)),
+                                   ("v", _lib.quant(2, vd), (V8, V8s))):
+        assert torch.equal(gs.cpu(), s), f"{name} scales differ"
+        assert _eq8(gc, c), f"{name} codes differ"
+    gc, gs, gd = _lib.quant_do(dod, od)
+    assert torch.equal(gs.cpu(), dO8s) and _eq8(gc, dO8) and torch.equal(gd.cpu(), dlt)
+    gc2, gs2, none = _lib.quant_do(dod)
+    assert none is None and torch.equal(gs2, gs) and torch.equal(gc2.view(torch.uint8), gc.view(torch.uint8))
+
+
+@pytest.mark.parametrize("D", [128, 256])
+def test_golden_inputs(D):
+    q, k, v, dO, Oo = golden_inputs(D)
+    _check_all(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dO, Oo)
+
+
+@pytest.mark.parametrize("B,N,H,Hk,D", [(1, 256, 2, 2, 128), (2, 512, 8, 2, 128), (2, 384, 4, 1, 256)])
+def test_random_and_packed_views(B, N, H, Hk, D):
+    g = torch.Generator("cpu").manual_seed(11)
+    qkv = torch.randn(B, N, H + 2 * Hk, D, generator=g).to(torch.bfloat16)
+    q, k, v = qkv.split([H, Hk, Hk], dim=2)
+    dO = (torch.randn(B, N, H, D, generator=g) * 0.01).to(torch.bfloat16)
+    Oo = torch.randn(B, N, H, D, generator=g).to(torch.bfloat16)
+    # device tensors keep the packed strides
+    qkv_d = qkv.cuda()
+    qd, kd, vd = qkv_d.split([H, Hk, Hk], dim=2)
+    Q8, Q8s = O.quant_q(q.transpose(1, 2))
+    K8, K8s, km = O.quant_k(k.transpose(1, 2))
+    V8, V8s = O.quant_v(v.transpose(1, 2))
+    gkm = _lib.kmean(kd)
+    assert torch.equal(gkm.cpu(), km)
+    for (gc, gs), (c, s) in ((_lib.quant(0, qd), (Q8, Q8s)), (_lib.quant(1, kd, gkm), (K8, K8s)), (_lib.quant(2, vd), (V8, V8s))):
+        assert torch.equal(gs.cpu(), s) and _eq8(gc, c)
+    _check_all(q.contiguous(), k.contiguous(), v.contiguous(), dO, Oo)
+
+
+def test_expanded_grad_and_saturation():
+    """A stride-0 expanded dO (the gradient of o.sum()) is made unit-stride by the wrapper; an all-equal block saturates
+    every code at +-448 / scale."""
+    B, N, H, D = 1, 256, 2, 128
+    dO = torch.ones(1, 1, 1, 1, dtype=torch.bfloat16).expand(B, N, H, D)
+    gc, gs, _ = _lib.quant_do(dO.cuda())
+    c, s = O.quant_do(dO.contiguous())
+    assert torch.equal(gs.cpu(), s) and _eq8(gc, c)
+    assert (gc.float() == 448.0).all()
+
+
+def test_gqa_fold():
+    g = torch.Generator("cpu").manual_seed(5)
+    x = torch.randn(2, 256, 8, 128, generator=g).to(torch.bfloat16)
+    out = _lib.gqa_fold(x.cuda(), 2).cpu()
+    ref = x.view(2, 256, 2, 4, 128).float().sum(3).to(torch.bfloat16)
+    assert (out.float() - ref.float()).abs().max() <= 2 * ref.float().abs().max() * 2 ** -8
+    seq = x.view(2, 256, 2, 4, 128).float()
+    acc = ((seq[:, :, :, 0] + seq[:, :, :, 1]) + seq[:, :, :, 2]) + seq[:, :, :, 3]
+    assert torch.equal(out, acc.to(torch.bfloat16))
