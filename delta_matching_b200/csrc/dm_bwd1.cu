@@ -1,0 +1,303 @@
+// Pass 1 of the backward, head_dim 128: dK and dV per query head, plus the e4m3 dS' code tiles and their psi scales for
+// pass 2 (csrc/mainloop_bwd_sm90_fp8r.hpp:695-952 of the reference, restated for tcgen05).
+//
+// One CTA = one 128-key block of one (batch, query head); 256 threads; 64-row m-blocks ascending from the causal start.
+// Everything is computed transposed (keys x rows), so tensor-memory lane = key and the per-key scales are per-thread
+// constants.  Per m-block:
+//   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each, into one of two (S | dP) tensor-memory buffers;
+//                                  issued one m-block ahead so they run under the arithmetic below
+//   P-hat, dS' = P-hat (dP descaled - delta k8s), tile amax over the 64 x 128 tile (all 256 threads), psi by the F2 / F2b
+//   rules, codes P-hat8 = e4m3(P-hat), dS'8 = e4m3(dS' / psi) written to two swizzled K-major tiles [key][row]
+//   dV_tmp (+)= P-hat8^T dO8       M128 N128 K32 x 2, zero-initialised on the first m-block of a 128-row dO scale block
+//   dK_tmp  = dS'8^T Q8            M128 N128 K32 x 2, zero-initialised
+//   dK += dK_tmp * (psi 2^-8 q8sc)  and, once per 128-row block,  dV += dV_tmp * (2^-8 do8sc)    in registers
+// Q8 / dO8 m-block tiles serve twice: K-major as the B operand of S^T / dP^T and MN-major as the B operand of dK / dV.
+// The finished 128 x 128 dS' tile ([key][row], the layout pass 2 reads as an MN-major A operand) leaves by a TMA store.
+#include "dm_attn_common.cuh"
+#include "dm_host.h"
+
+namespace dmh {
+int check_shape(const DmShape& s, int h0, int hcount, char* err, size_t errlen);
+}
+
+namespace {
+
+constexpr int kTile = 128 * 128;
+constexpr int kHalf = 64 * 128;
+constexpr int kStages = 3;
+
+struct Bwd1Smem {
+    alignas(1024) uint8_t k[kTile];
+    alignas(1024) uint8_t v[kTile];
+    alignas(1024) uint8_t q[kStages][kHalf];
+    alignas(1024) uint8_t dO[kStages][kHalf];
+    alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]
+    alignas(1024) uint8_t ds[kTile];      // dS' codes, same layout
+    float rc[2][64];                      // 8 - lse * log2e per row of the m-block
+    float dlk[2][2][64];                  // delta * k8s(group) per row
+    float amax[8];
+    uint64_t bar_kv, bar_qdo[kStages], bar_sp[2], bar_dkv;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct Bwd1Params {
+    const float* q8s;
+    const float* k8s;
+    const float* v8s;
+    const float* do8s;
+    const float* lse;
+    const float* delta;
+    __nv_bfloat16* dk;
+    __nv_bfloat16* dv;
+    float* psi;
+    int H, Hk, N, h0, hcount, causal;
+    int* status;
+};
+
+__global__ void __launch_bounds__(256, 1)
+bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_ds, const Bwd1Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    Bwd1Smem& s = *reinterpret_cast<Bwd1Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;                      // column half: rows [32 g, 32 g + 32) of S^T, d [64 g, 64 g + 64) of dK / dV
+    const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
+    const int kgrp = key >> 6;                    // 64-key scale group inside the block
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const int bhl = hc.b * p.hcount + (hc.h - p.h0);
+    const int nbn = p.N / 128, nbm = p.N / 64;
+    const int J = blockIdx.x;                     // key block; J = 0 has the most m-blocks when causal and is launched first
+    const int m_lo = p.causal ? 2 * J : 0;
+    const int n_it = nbm - m_lo;
+    dm::WaitCtx wc{&s.abort_flag, p.status};
+
+    if (tid == 0) {
+        s.abort_flag = 0;
+        dm::mbar_init(&s.bar_kv, 1);
+        for (int i = 0; i < kStages; ++i) dm::mbar_init(&s.bar_qdo[i], 1);
+        dm::mbar_init(&s.bar_sp[0], 1);
+        dm::mbar_init(&s.bar_sp[1], 1);
+        dm::mbar_init(&s.bar_dkv, 1);
+        dm::fence_mbar_init();
+    }
+    if (warp == 0) dm::tmem_alloc(&s.tmem_base, 512);
+    dm::tc_fence_before();
+    __syncthreads();
+    dm::tc_fence_after();
+    const uint32_t tmem = s.tmem_base;
+    const uint32_t t_dv = tmem + 256, t_dk = tmem + 384;
+    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+    const int q_row0 = hc.bh * p.N;
+    const int kv_row0 = hc.bhk * p.N + J * 128;
+    constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
+    constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
+
+    auto load_qdo = [&](int it) {
+        const int st = it % kStages, mb = m_lo + it;
+        dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kHalf);
+        dm::tma_load_2d(s.q[st], &tm_q, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
+        dm::tma_load_2d(s.dO[st], &tm_do, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
+    };
+    auto issue_sp = [&](int it) {   // S^T and dP^T of iteration `it` into buffer it & 1
+        const int st = it % kStages;
+        dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
+        dm::tc_fence_after();
+        const uint32_t ka = dm::smem_u32(s.k), va = dm::smem_u32(s.v), qa = dm::smem_u32(s.q[st]), da = dm::smem_u32(s.dO[st]);
+        const uint32_t t_s = tmem + (it & 1) * 128, t_dp = t_s + 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            dm::umma_e4m3(t_s, dm::smem_desc_sw128(ka + 32 * k), dm::smem_desc_sw128(qa + 32 * k), idesc_sp, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            dm::umma_e4m3(t_dp, dm::smem_desc_sw128(va + 32 * k), dm::smem_desc_sw128(da + 32 * k), idesc_sp, k > 0);
+        dm::umma_commit(&s.bar_sp[it & 1]);
+    };
+
+    if (tid == 0) {
+        dm::mbar_expect_tx(&s.bar_kv, 2 * kTile);
+        dm::tma_load_2d(s.k, &tm_k, 0, kv_row0, &s.bar_kv);
+        dm::tma_load_2d(s.v, &tm_v, 0, kv_row0, &s.bar_kv);
+        for (int i = 0; i < kStages && i < n_it; ++i) load_qdo(i);
+        dm::mbar_wait(&s.bar_kv, 0, wc);
+        issue_sp(0);
+    }
+
+    const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
+    const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
+    float g_max = 0.f;
+    float dk_acc[64], dv_acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) { dk_acc[i] = 0.f; dv_acc[i] = 0.f; }
+
+    for (int it = 0; it < n_it; ++it) {
+        const int mb = m_lo + it, st = it % kStages, par = mb & 1, sb = it & 1;
+        if (tid == 0 && it + 1 < n_it) issue_sp(it + 1);
+        // per-row constants of this m-block (threads 0..127: row = tid & 63, scale group = tid >> 6)
+        if (tid < 128) {
+            const int r = tid & 63, grp = tid >> 6;
+            const int64_t gi = (int64_t)hc.bh * p.N + mb * 64 + r;
+            const float kk = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + grp];
+            s.dlk[sb][grp][r] = p.delta[gi] * kk;
+            if (grp == 0) s.rc[sb][r] = dm::phat_row_const(p.lse[gi]);
+        }
+        const float q8sc = p.q8s[(int64_t)hc.bh * nbn + (mb >> 1)];
+        const float do8sc = p.do8s[(int64_t)hc.bh * nbn + (mb >> 1)];
+        const float dsc = dm::descale_log2(q8sc, k8s_t);
+        const float dpk = do8sc * v8s_t * k8s_t;
+        __syncthreads();                                   // row constants visible
+        dm::mbar_wait(&s.bar_sp[sb], (it >> 1) & 1, wc);
+        dm::tc_fence_after();
+
+        // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory
+        float sv[32], ds[32];
+        dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
+        dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128 + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
+        dm::tmem_ld_wait();
+        const bool diag = p.causal && (mb >> 1) == J;
+        const int row_in_pair = par * 64 + g * 32;         // row offset of column 0 inside the 128-row pair
+        float amax = 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float ph = dm::phat(sv[c], dsc, s.rc[sb][g * 32 + c]);
+            if (diag && key > row_in_pair + c) ph = 0.f;
+            sv[c] = ph;
+            ds[c] = ph * (ds[c] * dpk - s.dlk[sb][kgrp][g * 32 + c]);
+            amax = fmaxf(amax, fabsf(ds[c]));
+        }
+        {
+            uint32_t w[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) w[c] = dm::cvt_e4m3x4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
+            *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) s.amax[warp] = amax;
+        if (tid == 0 && par == 0) dm::tma_store_wait_read0();   // the previous pair's dS' tile has left shared memory
+        dm::tc_fence_before();
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[i]);
+        const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
+        const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
+        const float psi = fmaxf(psi_raw, g_max * (256.0f * 1e-8f) / q8sc);
+        const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
+        const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
+        g_max = fmaxf(g_max, g_cur);
+        if (tid == 0) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
+
+        // ---- phase 2: dS' codes
+        {
+            uint32_t w[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
+            *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        dm::fence_proxy_async_smem();
+        __syncthreads();
+
+        if (tid == 0) {
+            dm::tc_fence_after();
+            const uint32_t pa = dm::smem_u32(s.pt) + par * 64, sa = dm::smem_u32(s.ds) + par * 64;
+            const uint32_t qa = dm::smem_u32(s.q[st]), da = dm::smem_u32(s.dO[st]);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                dm::umma_e4m3(t_dv, dm::smem_desc_sw128(pa + 32 * k), dm::smem_desc_sw128(da + 4096 * k), idesc_dkv, (par != 0) || k > 0);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                dm::umma_e4m3(t_dk, dm::smem_desc_sw128(sa + 32 * k), dm::smem_desc_sw128(qa + 4096 * k), idesc_dkv, k > 0);
+            dm::umma_commit(&s.bar_dkv);
+            if (par == 1) {   // the 128 x 128 dS' tile of this row pair is complete
+                dm::tma_store_2d(&tm_ds, 0, (int)((((int64_t)bhl * nbn + (mb >> 1)) * nbn + J) * 128), s.ds);
+                dm::tma_store_commit();
+            }
+        }
+        dm::mbar_wait(&s.bar_dkv, it & 1, wc);
+        dm::tc_fence_after();
+        if (tid == 0 && it + kStages < n_it) load_qdo(it + kStages);   // this stage's Q / dO tiles are free
+        {
+            float t[64];
+            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
+            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
+            dm::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_cur, dk_acc[i]);
+            if (par == 1) {
+                const float f = dm::kMoInv * do8sc;
+                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
+                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
+                dm::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 64; ++i) dv_acc[i] = fmaf(t[i], f, dv_acc[i]);
+            }
+        }
+        dm::tc_fence_before();
+    }
+
+    // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
+    if (tid == 0) dm::tma_store_wait_all0();
+    const float ik = 1.0f / k8s_t;
+    const int n_glob = J * 128 + key;
+    const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 128 + g * 64;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        uint32_t wk[4], wv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[8 * c + 2 * e] * ik, dk_acc[8 * c + 2 * e + 1] * ik);
+            __nv_bfloat162 b = __floats2bfloat162_rn(dv_acc[8 * c + 2 * e], dv_acc[8 * c + 2 * e + 1]);
+            wk[e] = *reinterpret_cast<uint32_t*>(&a);
+            wv[e] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        reinterpret_cast<uint4*>(p.dk + off)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+        reinterpret_cast<uint4*>(p.dv + off)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+    }
+    __syncthreads();
+    if (warp == 0) dm::tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+extern "C" int dm_bwd_workspace_bytes(DmShape sh, int32_t hcount, size_t* ds8_bytes, size_t* psi_bytes) {
+    if (!ds8_bytes || !psi_bytes || sh.N <= 0 || sh.N % 128 || sh.B <= 0 || hcount <= 0) return DM_ERR_ARG;
+    const size_t kb = sh.D == 128 ? 128 : 64;
+    *ds8_bytes = (size_t)sh.B * hcount * sh.N * sh.N;
+    *psi_bytes = (size_t)sh.B * hcount * (sh.N / 64) * (sh.N / kb) * sizeof(float);
+    return DM_OK;
+}
+
+extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                                const float* v8s, const float* do8s, const float* lse, const float* delta, DmShape sh, int32_t h0,
+                                int32_t hcount, void* dk, void* dv, void* ds8_ws, float* psi_ws, void* stream, char* err, size_t errlen) {
+    int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
+    if (rc) return rc;
+    const void* ptrs[] = {q8, k8, v8, do8, q8s, k8s, v8s, do8s, lse, delta, dk, dv, ds8_ws, psi_ws};
+    const char* names[] = {"q8", "k8", "v8", "do8", "q8s", "k8s", "v8s", "do8s", "lse", "delta", "dk", "dv", "ds8_ws", "psi_ws"};
+    for (int i = 0; i < 14; ++i)
+        if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
+    DM_REQUIRE(dmh::aligned16(dk) && dmh::aligned16(dv) && dmh::aligned16(ds8_ws), DM_ERR_ARG, "outputs and workspace must be 16-byte aligned");
+    DM_REQUIRE(sh.D == 128, DM_ERR_UNSUPPORTED, "backward pass 1 for head_dim %d is not built yet (head_dim 128 only)", sh.D);
+    const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
+    DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads (got %llu tiles)",
+               (unsigned long long)ntiles);
+    CUtensorMap tq, td, tk, tv, ts;
+    if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&td, do8, 128, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tv, v8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&ts, ds8_ws, 128, ntiles * 128, 128, err, errlen))) return rc;
+    int* status = dmh::device_status_word(err, errlen);
+    if (!status) return DM_ERR_CUDA;
+    Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), psi_ws,
+                 sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
+    const int smem = (int)sizeof(Bwd1Smem) + 1024;
+    DM_CUDA(cudaFuncSetAttribute(bwd1_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    bwd1_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
