@@ -1,0 +1,367 @@
+"""Benchmark of the Delta-Matching fp8 attention hot path (forward + backward, quantizers included) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 2] [--impl reference]
+
+One "step" = `o = dm_attn_func(q, k, v, causal, mode); o.backward(dO)` on one batch of synthetic input (the reference's
+own protocol, benchmarks/bench.py:52-55 of the reference: the whole composition, producers included).  The default
+workload is BASELINE config 2 (B=2, N=2048, H=16, Hk=16, D=128, causal, matched); --config 1..5 selects another.
+Prints ONE JSON line (rank 0).  Keys:
+  value        whole-job TFLOP/s over all ranks with inputs resident in HBM (algorithmic FLOPs: 7 matmuls of 2*N*N*D per
+               head, halved when causal; pass-0 recomputation and softmax work are not counted)
+  e2e          the same metric through the public API with HOST pinned buffers: H2D of q, k, v, dO and D2H of O, dQ, dK,
+               dV inside the timed region
+  roofline     the dominant kernel's algorithmic TFLOP/s (CUDA events around that kernel, live) against the measured dense
+               FP8 GEMM peak of this GPU (torch._scaled_mm, measured in this run) -- the bf16 peak of MEASURED_PEAKS.json and
+               the nominal 4500 TFLOP/s are reported beside it
+  cpu_baseline the CPU oracle (a PyTorch restatement of the reference numerics) timed on the host cores on a bounded
+               sample of the same workload
+With --impl reference the CPU oracle itself is the timed arm (the reference's CUDA kernels are Hopper-only and cannot run
+here); under torchrun only rank 0 runs it.  Multi-GPU: one process per GPU, the (batch x head) work is replicated per
+rank with its own seed (weak scaling, no data-path collective), time = max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {  # BASELINE.json configs: (B, N, H, Hk, D, causal, mode)
+    1: (1, 256, 2, 2, 128, True, "matched"),
+    2: (2, 2048, 16, 16, 128, True, "matched"),
+    3: (4, 4096, 32, 8, 128, True, "matched"),
+    4: (2, 4096, 16, 4, 256, False, "stale"),
+    5: (1, 65536, 32, 8, 128, True, "matched"),
+}
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def algorithmic_flops(B, N, H, D, causal):
+    return (7 if causal else 14) * B * H * N * N * D
+
+
+def make_host_inputs(cfg, seed):
+    B, N, H, Hk, D, causal, mode = cfg
+    g = torch.Generator("cpu").manual_seed(seed)
+    mk = lambda h: torch.randn(B, N, h, D, generator=g).to(torch.bfloat16).pin_memory()
+    q, k, v, dO = mk(H), mk(Hk), mk(Hk), mk(H)
+    return q, k, v, dO
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv:
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.nv:
+            self.t.join(timeout=1)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def measure_fp8_peak(dev):
+    """Dense e4m3 x e4m3 GEMM 8192^3 through torch._scaled_mm: best of 10 (the denominator of the roofline fraction)."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        for _ in range(3):
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def cpu_oracle_time(cfg, budget_s=25.0):
+    """The CPU oracle on a bounded sample of the workload: whole heads of batch 0 (heads and batches are independent, so the
+    full-workload time is sample time x factor).  Returns (TFLOP/s of the sample, cores, description, seconds)."""
+    from oracle import dm_oracle as O
+    B, N, H, Hk, D, causal, mode = cfg
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    rep = H // Hk
+    # per-KV-group cost estimate from a small probe, then pick how many KV groups fit the budget
+    groups = 1
+    n_s = N if N <= 8192 else 8192
+    q, k, v, dO = O.make_inputs(1, n_s, rep * groups, groups, D, 77)
+    t0 = time.perf_counter()
+    O.attention_fwd_bwd(q, k, v, dO, causal, mode)
+    dt = time.perf_counter() - t0
+    fl = algorithmic_flops(1, n_s, rep * groups, D, causal)
+    if dt < budget_s / 4 and Hk > 1 and n_s == N:
+        groups = int(min(Hk, max(1, (budget_s / 2) // max(dt, 1e-3))))
+        q, k, v, dO = O.make_inputs(1, n_s, rep * groups, groups, D, 78)
+        t0 = time.perf_counter()
+        O.attention_fwd_bwd(q, k, v, dO, causal, mode)
+        dt = time.perf_counter() - t0
+        fl = algorithmic_flops(1, n_s, rep * groups, D, causal)
+    factor = algorithmic_flops(B, N, H, D, causal) / fl
+    desc = (f"oracle fwd+bwd on batch 0, {groups} of {B * Hk} KV groups ({rep * groups} query heads), seqlen {n_s} of {N}; "
+            f"full workload = sample x {factor:.1f} by FLOPs")
+    return fl / dt / 1e12, cores, desc, dt
+
+
+def run_reference_arm(args, cfg, rank, world):
+    if rank != 0:
+        return
+    B, N, H, Hk, D, causal, mode = cfg
+    vals, desc, cores = [], "", 1
+    for i in range(args.warmup + args.steps):
+        tf, cores, desc, dt = cpu_oracle_time(cfg, budget_s=12.0)
+        if i >= args.warmup:
+            vals.append((tf, dt))
+    tf = statistics.mean(v[0] for v in vals)
+    ms = statistics.mean(v[1] for v in vals) * 1e3
+    line = {"impl": "reference", "metric": "fp8_attn_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "e4m3", "data": "synthetic",
+            "config": workload_config(args.config, cfg, "host (CPU oracle: PyTorch restatement of the reference numerics; the "
+                                      "reference's own kernels are sm_90a-only and cannot run on this machine)"),
+            "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(idx, cfg, where):
+    B, N, H, Hk, D, causal, mode = cfg
+    return {"workload": f"BASELINE config {idx}: B={B} N={N} H={H} Hk={Hk} D={D} {'causal' if causal else 'full'} {mode}, "
+                        f"fwd+bwd incl. quantizers", "B": B, "N": N, "H": H, "Hk": Hk, "D": D, "causal": causal, "mode": mode,
+            "parallelism": where, "l2": "flushed between timed iterations (256 MiB write)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", type=int, default=2)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    cfg = CONFIGS[args.config]
+    B, N, H, Hk, D, causal, mode = cfg
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank, world)
+        return
+
+    import torch.distributed as dist
+    import delta_matching_b200 as dm
+    from delta_matching_b200 import _lib
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # count the library's kernel launches per call (one entry point can launch more than one kernel)
+    launches = {"n": 0}
+    per_call = {"dm_kmean": 2, "dm_quant": 1, "dm_quant_do": 1, "dm_fwd_fp8": 1, "dm_delta_fp8": 1, "dm_bwd_fp8_pass1": 1,
+                "dm_bwd_fp8_pass2": 1, "dm_gqa_fold": 1}
+    orig_call = _lib._call
+
+    def counting_call(name, *a):
+        launches["n"] += per_call.get(name, 0)
+        return orig_call(name, *a)
+    _lib._call = counting_call
+
+    hq, hk, hv, hdo = make_host_inputs(cfg, 1000 + args.config + 17 * rank)
+    q, k, v, dO = (t.to(dev) for t in (hq, hk, hv, hdo))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
+    flops = algorithmic_flops(B, N, H, D, causal)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        o = dm.dm_attn_func(q, k, v, causal=causal, mode=mode)
+        o.backward(dO)
+        return o
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    launches["n"] = 0
+    times = []
+    with ClockSampler(local) as clk:
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        sync_all()
+    n_launch = launches["n"]
+    total_ms = sum(times)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_step = total_ms / args.steps
+    value = world * flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end with host buffers (H2D of q, k, v, dO; D2H of O, dQ, dK, dV inside the timed region)
+    outs = [torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory(), torch.empty_like(hk).pin_memory(),
+            torch.empty_like(hv).pin_memory()]
+
+    def e2e_step():
+        dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+        dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
+        o = dm.dm_attn_func(dq_, dk_, dv_, causal=causal, mode=mode)
+        o.backward(ddo)
+        for dst, src in zip(outs, (o.detach(), dq_.grad, dk_.grad, dv_.grad)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    e2e_times = []
+    for _ in range(max(3, args.steps // 2)):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_step()
+        e1.record()
+        e1.synchronize()
+        e2e_times.append(e0.elapsed_time(e1))
+    e2e_ms = statistics.mean(e2e_times)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    nbytes = lambda t: t.numel() * t.element_size()
+    e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": sum(nbytes(t) for t in (hq, hk, hv, hdo)), "d2h_bytes_per_step": sum(nbytes(t) for t in outs)}
+
+    # ---- per-kernel timing (CUDA events around each library call, same inputs, L2 flushed) and the roofline
+    roof, kernels = None, {}
+    if rank == 0:
+        with torch.no_grad():
+            qf, kf, vf = q.detach(), k.detach(), v.detach()
+            reps = max(5, min(args.steps, 10))
+            acc = {}
+
+            def timed(name, fn):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = fn()
+                e1.record()
+                acc.setdefault(name, []).append((e0, e1))
+                return r
+            for _ in range(reps):
+                flush.fill_(1)
+                Q8, Q8s = timed("quant_q", lambda: _lib.quant(0, qf))
+                km = timed("kmean", lambda: _lib.kmean(kf))
+                K8, K8s = timed("quant_k", lambda: _lib.quant(1, kf, km))
+                V8, V8s = timed("quant_v", lambda: _lib.quant(2, vf))
+                O_, lse = timed("fwd", lambda: _lib.fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal))
+                dO8, dO8s, dl = timed("quant_do", lambda: _lib.quant_do(dO, None if mode == "matched" else O_))
+                if mode == "matched":
+                    dl = timed("pass0_delta", lambda: _lib.delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal))
+                hp = dm.split._bwd_heads_per_call(B, H, Hk, H // Hk, N)
+                if hp >= H:
+                    dk_, dv_, ws = timed("pass1", lambda: _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, dl, B, H, Hk, causal))
+                    timed("pass2", lambda: _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal))
+            torch.cuda.synchronize()
+            kernels = {n: statistics.mean(a.elapsed_time(b) for a, b in ev) for n, ev in acc.items()}
+        u = flops / 7.0                      # one matmul's FLOPs (causal halving already inside `flops`)
+        alg = {"fwd": 2 * u, "pass1": 4 * u, "pass2": 1 * u}
+        fp8_peak = measure_fp8_peak(dev)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        cand = {n: kernels[n] for n in alg if n in kernels}
+        if cand:
+            top = max(cand, key=cand.get)
+            achieved = alg[top] / (kernels[top] * 1e-3) / 1e12
+            peak = fp8_peak or NOMINAL_FP8_TFLOPS
+            roof = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_source": "torch._scaled_mm e4m3 8192^3 best of 10, measured in this run" if fp8_peak else "nominal dense FP8",
+                    "frac_of_nominal_fp8_4500": achieved / NOMINAL_FP8_TFLOPS,
+                    "frac_of_measured_bf16": achieved / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
+                    "traffic": None, "kernel_ms": kernels,
+                    "per_kernel_tflops": {n: alg[n] / (kernels[n] * 1e-3) / 1e12 for n in cand}}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tf, cores, desc, dt = cpu_oracle_time(cfg)
+        cpu = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc, "sample_seconds": dt}
+
+    if rank == 0:
+        line = {"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "e4m3", "data": "synthetic",
+                "config": workload_config(args.config, cfg, f"dp{world} over (batch x head), no collective"),
+                "tflops_per_gpu": value / world, "frac_of_nominal_fp8_per_gpu": value / world / NOMINAL_FP8_TFLOPS,
+                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -19,6 +19,7 @@ from __future__ import annotations
 import torch
 
 from .attn import dm_attn_func_bhnd, dm_attn_func_plain
+from . import split  # noqa: F401  (DM_BWD_* environment knobs live there)
 from .core import blocks
 
 __version__ = "0.1.0"

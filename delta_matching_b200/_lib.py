@@ -115,6 +115,14 @@ def blocks(D: int):
     return (64, 32) if D >= 256 else (128, 64)
 
 
+def _device_of(*ts):
+    """The CUDA device the call runs on: the first CUDA tensor's; host tensors are left for the library to refuse."""
+    for t in ts:
+        if t is not None and t.is_cuda:
+            return t.device
+    return torch.device("cuda", torch.cuda.current_device())
+
+
 def _unit_lane(t):
     return t if t.stride(-1) == 1 else t.contiguous()
 
@@ -167,7 +175,7 @@ def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=
     """O (B, N, H, D) bf16 and LSE [B*H, N] fp32; with a head range only those heads are written."""
     BH, N, D = Q8.shape
     hcount = H if hcount is None else hcount
-    dev = Q8.device
+    dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
         if out is None:
             o = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
@@ -182,7 +190,7 @@ def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=
 def delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, h0=0, hcount=None, out=None):
     BH, N, D = Q8.shape
     hcount = H if hcount is None else hcount
-    dev = Q8.device
+    dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
         delta = torch.empty(B * H, N, device=dev, dtype=torch.float32) if out is None else out
         _call("dm_delta_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
@@ -202,7 +210,7 @@ def bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal
     """dK, dV (B, N, H, D) bf16 per query head plus the dS' / psi workspace for pass 2."""
     BH, N, D = Q8.shape
     hcount = H if hcount is None else hcount
-    dev = Q8.device
+    dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
         if out is None:
             dk = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
@@ -240,7 +248,7 @@ def gqa_fold(x_bnhd, Hk):
 
 def bwd_dbg_rowsum(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal):
     BH, N, D = Q8.shape
-    dev = Q8.device
+    dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
         rows = torch.empty(B * H, N, device=dev, dtype=torch.float32)
         rabs = torch.empty(B * H, N, device=dev, dtype=torch.float32)

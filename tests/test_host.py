@@ -1,0 +1,88 @@
+"""Host-side logic that needs no GPU: the library loads and exports every symbol declared in include/dm_b200.h, the C ABI
+validates shapes before touching the device, the head-group split decision, and the argument checks of the public API
+that precede any device work."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+import delta_matching_b200 as dm
+from delta_matching_b200 import _lib, split
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "dm_b200.h")).read()
+    declared = set(re.findall(r"\b(dm_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    handle = C.CDLL(_lib.library_path())
+    for name in declared:
+        assert hasattr(handle, name), f"{name} is declared in include/dm_b200.h but not exported"
+    assert set(_lib.EXPORTS) == declared, (set(_lib.EXPORTS) ^ declared)
+    assert "sm_100a" in _lib.build_info()
+
+
+def test_shape_validation_happens_before_any_device_work():
+    lib = _lib.lib()
+    err = C.create_string_buffer(256)
+    bad = [(_lib.DmShape(1, 4, 4, 1000, 128, 1), "seqlen"), (_lib.DmShape(1, 4, 3, 512, 128, 1), "nheads"),
+           (_lib.DmShape(1, 4, 4, 512, 64, 1), "head_dim"), (_lib.DmShape(0, 4, 4, 512, 128, 1), "empty"),
+           (_lib.DmShape(70000, 1, 1, 512, 128, 1), "65535")]
+    for shp, word in bad:
+        rc = lib.dm_fwd_fp8(None, None, None, None, None, None, shp, 0, shp.H, None, None, None, err, len(err))
+        assert rc == -1 and word in err.value.decode(), (rc, err.value)
+    rc = lib.dm_fwd_fp8(None, None, None, None, None, None, _lib.DmShape(1, 4, 4, 512, 128, 1), 2, 4, None, None, None, err, len(err))
+    assert rc == -1 and "head range" in err.value.decode()
+    a, b = C.c_size_t(0), C.c_size_t(0)
+    assert lib.dm_bwd_workspace_bytes(_lib.DmShape(1, 16, 16, 8192, 128, 1), 16, C.byref(a), C.byref(b)) == 0
+    assert a.value == 2 ** 30 and b.value == 16 * 128 * 64 * 4          # 1 GiB at batch 1, 16 heads, N = 8192
+    assert lib.dm_kmean_scratch_bytes(4, 8, 4096, 128) == 4 * 8 * 64 * 128 * 4
+
+
+def test_head_group_split_decision(monkeypatch):
+    monkeypatch.setattr(split, "_BWD_GROUPS", "auto")
+    monkeypatch.setattr(split, "_BWD_WS_LIMIT", 8 * 2 ** 30)
+    assert split._bwd_heads_per_call(1, 16, 4, 4, 8192) == 16            # 1 GiB: no split
+    assert split._bwd_heads_per_call(4, 32, 8, 4, 4096) == 32            # config 3: 2 GiB
+    assert split._bwd_heads_per_call(1, 32, 8, 4, 65536) == 1            # config 5: 4 GiB per head
+    assert split._bwd_heads_per_call(1, 32, 8, 4, 32768) == 4            # 1 GiB per head: per KV group
+    monkeypatch.setattr(split, "_BWD_GROUPS", "kv")
+    assert split._bwd_heads_per_call(1, 16, 4, 4, 1024) == 4
+    monkeypatch.setattr(split, "_BWD_GROUPS", "head")
+    assert split._bwd_heads_per_call(1, 16, 4, 4, 1024) == 1
+    monkeypatch.setattr(split, "_BWD_GROUPS", "off")
+    assert split._bwd_heads_per_call(1, 32, 8, 4, 65536) == 32
+
+
+def test_argument_checks_that_precede_device_work():
+    q = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError, match="dropout"):
+        dm.flash_attn_func(q, q, q, 0.1, causal=True)
+    with pytest.raises(NotImplementedError, match="window"):
+        dm.flash_attn_func(q, q, q, causal=True, window_size=(128, 0))
+    with pytest.raises(NotImplementedError, match="softcap"):
+        dm.flash_attn_func(q, q, q, causal=True, softcap=30.0)
+    with pytest.raises(NotImplementedError, match="alibi"):
+        dm.flash_attn_func(q, q, q, causal=True, alibi_slopes=torch.zeros(2))
+    with pytest.raises(NotImplementedError, match="return_attn_probs"):
+        dm.flash_attn_func(q, q, q, causal=True, return_attn_probs=True)
+    with pytest.raises(ValueError, match="4-D"):
+        dm.dm_attn_func(q[0], q[0], q[0], causal=True)
+    with pytest.raises(ValueError, match="4-D"):
+        dm.dm_attn_func(None, q, q, causal=True)
+    with pytest.raises(TypeError, match="tensors"):
+        dm.dm_attn_func_bhnd(None, q, q)
+    with pytest.raises(ValueError, match="CUDA"):
+        dm.dm_attn_func(q, q, q, causal=True)
+    assert dm.blocks(128) == (128, 64) and dm.blocks(256) == (64, 32)
+    s = dm.kernel_version()
+    assert len(s["code_sha"]) == 12 and s["numerics"]["128"]
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setenv("DM_SO", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="does not exist"):
+        _lib.library_path()
