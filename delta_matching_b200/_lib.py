@@ -32,6 +32,8 @@ _SIGNATURES = {
     "dm_build_info": (C.c_char_p, []),
     "dm_kmean_scratch_bytes": (C.c_size_t, [C.c_int32] * 4),
     "dm_kmean": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
+    "dm_kmean_noalloc_max_bytes": (C.c_size_t, []),
+    "dm_kmean_noalloc": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_quant": (C.c_int, [C.c_int32, _P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, *_ERR]),
     "dm_quant_do": (C.c_int, [_P, DmStrides, _P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, *_ERR]),
     "dm_fwd_fp8": (C.c_int, [_P] * 6 + [DmShape, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
@@ -138,6 +140,17 @@ def kmean(k_bnhd):
         scratch = torch.empty(lib().dm_kmean_scratch_bytes(B, Hk, N, D) // 4, device=k_bnhd.device, dtype=torch.float32)
         _call("dm_kmean", _ptr(k_bnhd), _strides_bnhd(k_bnhd), B, Hk, N, D, _ptr(km), _ptr(scratch), _stream(k_bnhd.device))
     return km
+
+
+def kmean_noalloc(k_bnhd, out):
+    """The K mean through the entry point that allocates nothing: for callers whose own arena owns all device memory (or
+    that cannot take cudaMalloc's device-wide synchronisation), the partial sums live in a 4 MiB array inside the library.
+    `out` is the caller's [B*Hk, D] fp32 result tensor; the input must already have a unit head_dim stride.  Calls on one
+    device share that array, so do not let two of them overlap on the GPU."""
+    B, N, Hk, D = k_bnhd.shape
+    with torch.cuda.device(k_bnhd.device):
+        _call("dm_kmean_noalloc", _ptr(k_bnhd), _strides_bnhd(k_bnhd), B, Hk, N, D, _ptr(out), _stream(k_bnhd.device))
+    return out
 
 
 def quant(mode, x_bnhd, km=None):

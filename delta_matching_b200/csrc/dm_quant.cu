@@ -11,6 +11,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include <mutex>
+
 #include "dm_host.h"
 
 namespace {
@@ -297,6 +299,65 @@ extern "C" int dm_gqa_fold(const void* x, int32_t B, int32_t N, int32_t H, int32
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     gqa_fold_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(x), static_cast<uint4*>(out), total, H, Hk, D);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+// ---- K mean without any allocation ------------------------------------------------------------------------------------
+// Some callers cannot allocate device memory at all: a training process that has handed the whole of HBM to its own
+// arena (so a raw cudaMalloc from a library would fail or steal from it), or a latency-critical loop that must not hit
+// cudaMalloc's device-wide synchronisation.  For them dm_kmean_noalloc keeps the per-chunk partial sums in a fixed array
+// inside the library image.  Every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr size_t kNoAllocMaxFloats = (size_t)1 << 20;   // 4 MiB: B * Hk * (N / 64) * D floats, e.g. 8 KV heads x 65536 keys x 128
+static __device__ __align__(256) float g_kmean_noalloc_scratch[kNoAllocMaxFloats];
+
+// In host code the array's name is only a handle; the device address comes from cudaGetSymbolAddress, asked once per
+// device with that device current and cached.
+static std::mutex g_noalloc_mu;
+static float* g_noalloc_ptr[64] = {nullptr};
+
+static int noalloc_scratch(float** out, char* err, size_t errlen) {
+    int dev = -1;
+    DM_CUDA(cudaGetDevice(&dev));
+    DM_REQUIRE(dev >= 0 && dev < 64, DM_ERR_ARG, "device index %d is out of range", dev);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        DM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_kmean_noalloc_scratch));
+        DM_REQUIRE(p != nullptr, DM_ERR_CUDA, "cudaGetSymbolAddress returned a NULL scratch address");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return DM_OK;
+}
+
+extern "C" size_t dm_kmean_noalloc_max_bytes(void) { return kNoAllocMaxFloats * sizeof(float); }
+
+extern "C" int dm_kmean_noalloc(const void* k, DmStrides ks, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, void* stream,
+                                char* err, size_t errlen) {
+    int rc = check_geometry(B, Hk, N, D, err, errlen);
+    if (rc) return rc;
+    const size_t need = dm_kmean_scratch_bytes(B, Hk, N, D);
+    DM_REQUIRE(need <= kNoAllocMaxFloats * sizeof(float), DM_ERR_ARG,
+               "dm_kmean_noalloc: this shape needs %zu bytes of partial sums but the built-in scratch holds %zu "
+               "(B * Hk * (N / 64) * D floats must be at most %zu); use dm_kmean with caller-provided scratch",
+               need, kNoAllocMaxFloats * sizeof(float), kNoAllocMaxFloats);
+    if ((rc = dmh::check_device_ptr(k, "k", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(km, "km", err, errlen))) return rc;
+    if ((rc = check_strides(k, ks, D, "k", err, errlen))) return rc;
+    float* partials = nullptr;
+    if ((rc = noalloc_scratch(&partials, err, errlen))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(k);
+    // Every partial that the fold reads is written by the partial kernel of this same call first, so nothing in the
+    // shared array has to start at zero; what the previous call left there is simply overwritten.
+    if (D == 128) {
+        kmean_partial_kernel<128><<<dim3(N / 64 / 4, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
+        kmean_fold_kernel<128><<<B * Hk, 128, 0, st>>>(partials, N, km);
+    } else {
+        kmean_partial_kernel<256><<<dim3(N / 64 / 2, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
+        kmean_fold_kernel<256><<<B * Hk, 256, 0, st>>>(partials, N, km);
+    }
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

@@ -53,6 +53,20 @@ size_t dm_kmean_scratch_bytes(int32_t B, int32_t Hk, int32_t N, int32_t D);
 int dm_kmean(const void* k_bf16, DmStrides ks, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, float* partials,
              void* stream, char* err, size_t errlen);
 
+/* dm_kmean for callers that cannot allocate device memory -- a process whose own arena already owns all of HBM, or a loop
+ * that cannot afford cudaMalloc's device-wide synchronisation.  Same result as dm_kmean bit for bit, but the partial
+ * sums live in a 4 MiB array built into the library (dm_kmean_noalloc_max_bytes(); every GPU that loads the library
+ * holds it until the process exits), so the caller passes only the input and the output and the call makes no
+ * cudaMalloc / cudaFree.  Shapes with B * Hk * (N / 64) * D * 4 bytes above that limit are refused with DM_ERR_ARG.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device current)
+ * and caches it: make that first call before any stream capture.  All calls on a device share the one array, which keeps
+ * the previous call's contents (nothing needs clearing: each call overwrites every partial it reads); two calls that
+ * overlap on the GPU (different streams, no dependency) race on it, so serialise them.
+ * This entry point has no counterpart in the reference. */
+size_t dm_kmean_noalloc_max_bytes(void);
+int dm_kmean_noalloc(const void* k_bf16, DmStrides ks, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, void* stream,
+                     char* err, size_t errlen);
+
 /* Block quantizers: bf16 -> e4m3 codes + per-block fp32 scales.
  * mode 0 = Q (x * fp32(D^-0.5)), 1 = K (x - km[head, d]; `km` required), 2 = V (as is): scale = max(amax, 1e-30) / 448,
  * code = e4m3_rtne(clamp(x / scale, +-448)) with IEEE division.
