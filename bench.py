@@ -189,6 +189,8 @@ def main():
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="only warm-up and timed steps (for ncu captures): no e2e, no per-kernel "
+                    "timing, no peak measurement, no CPU baseline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     cfg = CONFIGS[args.config]
@@ -261,6 +263,12 @@ def main():
         total_ms = float(t.item())
     ms_step = total_ms / args.steps
     value = world * flops / (ms_step * 1e-3) / 1e12
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "ms_per_step": ms_step,
+                              "profile_only": True, "gpu_launches": n_launch}), flush=True)
+        return
 
     # ---- end to end with host buffers (H2D of q, k, v, dO; D2H of O, dQ, dK, dV inside the timed region)
     outs = [torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory(), torch.empty_like(hk).pin_memory(),

@@ -24,7 +24,7 @@ namespace {
 
 constexpr int kTile = 128 * 128;
 constexpr int kHalf = 64 * 128;
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 
 struct Bwd1Smem {
     alignas(1024) uint8_t k[kTile];
@@ -35,7 +35,7 @@ struct Bwd1Smem {
     alignas(1024) uint8_t ds[kTile];      // dS' codes, same layout
     float rc[2][64];                      // 8 - lse * log2e per row of the m-block
     float dlk[2][2][64];                  // delta * k8s(group) per row
-    float amax[8];
+    float amax[2][8];
     uint64_t bar_kv, bar_qdo[kStages], bar_sp[2], bar_dkv;
     uint32_t tmem_base;
     int abort_flag;
@@ -131,22 +131,66 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
     for (int i = 0; i < 64; ++i) { dk_acc[i] = 0.f; dv_acc[i] = 0.f; }
 
+    // Per-row constants of an m-block (8 - lse * log2e, delta * k8s(group)) are fetched one m-block ahead into registers by
+    // threads 0..127 (row = tid & 63, scale group = tid >> 6) and parked in shared memory at the end of the iteration.
+    const int rc_r = tid & 63, rc_grp = (tid >> 6) & 1;
+    const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + rc_grp];
+    auto fetch_rows = [&](int it, float& lse_v, float& dl_v) {
+        if (tid < 128) {
+            const int64_t gi = (int64_t)hc.bh * p.N + (int64_t)(m_lo + it) * 64 + rc_r;
+            lse_v = p.lse[gi];
+            dl_v = p.delta[gi];
+        }
+    };
+    auto park_rows = [&](int it, float lse_v, float dl_v) {
+        if (tid < 128) {
+            s.dlk[it & 1][rc_grp][rc_r] = dl_v * rc_kk;
+            if (rc_grp == 0) s.rc[it & 1][rc_r] = dm::phat_row_const(lse_v);
+        }
+    };
+    {
+        float a = 0.f, b = 0.f;
+        fetch_rows(0, a, b);
+        park_rows(0, a, b);
+    }
+    float q8sc_n = p.q8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
+    float do8sc_n = p.do8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
+    float g_prev = 0.f, f_prev = 0.f;
+    __syncthreads();
+
+    // Folds the dK_tmp (and, on the second m-block of a dO scale block, dV_tmp) products of iteration `it` into the register
+    // accumulators; called one iteration late so the MMAs have completed under the next m-block's arithmetic.
+    auto fold = [&](int it, float g_fold, float f_fold) {
+        dm::mbar_wait(&s.bar_dkv, it & 1, wc);
+        dm::tc_fence_after();
+        if (tid == 0 && it + kStages < n_it) load_qdo(it + kStages);   // that iteration's Q / dO stage is free
+        float t[64];
+        dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
+        dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
+        dm::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_fold, dk_acc[i]);
+        if (((m_lo + it) & 1) == 1) {
+            dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
+            dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
+            dm::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 64; ++i) dv_acc[i] = fmaf(t[i], f_fold, dv_acc[i]);
+        }
+    };
+
     for (int it = 0; it < n_it; ++it) {
         const int mb = m_lo + it, st = it % kStages, par = mb & 1, sb = it & 1;
         if (tid == 0 && it + 1 < n_it) issue_sp(it + 1);
-        // per-row constants of this m-block (threads 0..127: row = tid & 63, scale group = tid >> 6)
-        if (tid < 128) {
-            const int r = tid & 63, grp = tid >> 6;
-            const int64_t gi = (int64_t)hc.bh * p.N + mb * 64 + r;
-            const float kk = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + grp];
-            s.dlk[sb][grp][r] = p.delta[gi] * kk;
-            if (grp == 0) s.rc[sb][r] = dm::phat_row_const(p.lse[gi]);
+        float lse_n = 0.f, dl_n = 0.f;
+        if (it + 1 < n_it) fetch_rows(it + 1, lse_n, dl_n);
+        const float q8sc = q8sc_n, do8sc = do8sc_n;
+        if (it + 1 < n_it) {
+            q8sc_n = p.q8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
+            do8sc_n = p.do8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
         }
-        const float q8sc = p.q8s[(int64_t)hc.bh * nbn + (mb >> 1)];
-        const float do8sc = p.do8s[(int64_t)hc.bh * nbn + (mb >> 1)];
         const float dsc = dm::descale_log2(q8sc, k8s_t);
         const float dpk = do8sc * v8s_t * k8s_t;
-        __syncthreads();                                   // row constants visible
         dm::mbar_wait(&s.bar_sp[sb], (it >> 1) & 1, wc);
         dm::tc_fence_after();
 
@@ -175,12 +219,12 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        if (lane == 0) s.amax[warp] = amax;
+        if (lane == 0) s.amax[sb][warp] = amax;
         if (tid == 0 && par == 0) dm::tma_store_wait_read0();   // the previous pair's dS' tile has left shared memory
         dm::tc_fence_before();
         __syncthreads();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[i]);
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[sb][i]);
         const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
         const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
         const float psi = fmaxf(psi_raw, g_max * (256.0f * 1e-8f) / q8sc);
@@ -199,6 +243,12 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
         }
         dm::fence_proxy_async_smem();
+        // ---- the previous m-block's products, complete by now, go into the accumulators
+        if (it > 0) fold(it - 1, g_prev, f_prev);
+        g_prev = g_cur;
+        f_prev = dm::kMoInv * do8sc;
+        if (it + 1 < n_it) park_rows(it + 1, lse_n, dl_n);
+        dm::tc_fence_before();
         __syncthreads();
 
         if (tid == 0) {
@@ -217,27 +267,9 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 dm::tma_store_commit();
             }
         }
-        dm::mbar_wait(&s.bar_dkv, it & 1, wc);
-        dm::tc_fence_after();
-        if (tid == 0 && it + kStages < n_it) load_qdo(it + kStages);   // this stage's Q / dO tiles are free
-        {
-            float t[64];
-            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
-            dm::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_cur, dk_acc[i]);
-            if (par == 1) {
-                const float f = dm::kMoInv * do8sc;
-                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
-                dm::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 64; ++i) dv_acc[i] = fmaf(t[i], f, dv_acc[i]);
-            }
-        }
-        dm::tc_fence_before();
     }
+    fold(n_it - 1, g_prev, f_prev);
+    dm::tc_fence_before();
 
     // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
     if (tid == 0) dm::tma_store_wait_all0();
