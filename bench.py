@@ -188,6 +188,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank runs the whole config (its own seed); strong: the config's (batch x KV-head) groups "
+                         "are split across the ranks (delta_matching_b200.shard), e.g. config 5 sharded over heads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true", help="only warm-up and timed steps (for ncu captures): no e2e, no per-kernel "
                     "timing, no peak measurement, no CPU baseline")
@@ -222,6 +225,15 @@ def main():
         return orig_call(name, *a)
     _lib._call = counting_call
 
+    if args.scaling == "strong" and world > 1:
+        from delta_matching_b200.shard import kv_group_range
+        first, count = kv_group_range(B, Hk, rank, world)
+        rep = H // Hk
+        if count >= Hk:
+            B = count // Hk
+        else:
+            B, Hk, H = 1, count, count * rep
+        cfg = (B, N, H, Hk, D, causal, mode)          # this rank's shard; generated directly at shard size
     hq, hk, hv, hdo = make_host_inputs(cfg, 1000 + args.config + 17 * rank)
     q, k, v, dO = (t.to(dev) for t in (hq, hk, hv, hdo))
     q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
@@ -262,7 +274,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     ms_step = total_ms / args.steps
-    value = world * flops / (ms_step * 1e-3) / 1e12
+    value = world * flops / (ms_step * 1e-3) / 1e12       # every rank does `flops` (its whole config, or its equal shard)
 
     if args.profile:
         if rank == 0:
@@ -361,9 +373,11 @@ def main():
 
     if rank == 0:
         line = {"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
                 "dtype": "e4m3", "data": "synthetic",
-                "config": workload_config(args.config, cfg, f"dp{world} over (batch x head), no collective"),
+                "config": workload_config(args.config, CONFIGS[args.config], f"dp{world} over (batch x head), no collective" +
+                                          ("; the config's KV groups split across ranks" if args.scaling == "strong" else
+                                           "; every rank runs the whole config")),
                 "tflops_per_gpu": value / world, "frac_of_nominal_fp8_per_gpu": value / world / NOMINAL_FP8_TFLOPS,
                 "clocks": clk.summary(), "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)

@@ -1,18 +1,24 @@
 // Pass 1 of the backward, head_dim 128: dK and dV per query head, plus the e4m3 dS' code tiles and their psi scales for
 // pass 2 (csrc/mainloop_bwd_sm90_fp8r.hpp:695-952 of the reference, restated for tcgen05).
 //
-// One CTA = one 128-key block of one (batch, query head); 256 threads; 64-row m-blocks ascending from the causal start.
-// Everything is computed transposed (keys x rows), so tensor-memory lane = key and the per-key scales are per-thread
+// One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  384 threads:
+// warps 0..7 compute (232 registers each after setmaxnreg), warp 8 of the third warpgroup issues every TMA copy and every
+// tcgen05.mma (one lane) so that descriptor building and instruction issue never sit on the compute warps' path.  The two
+// sides meet only through mbarriers.
+// Everything is computed transposed (keys x rows): tensor-memory lane = key, so the per-key scales are per-thread
 // constants.  Per m-block:
-//   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each, into one of two (S | dP) tensor-memory buffers;
-//                                  issued one m-block ahead so they run under the arithmetic below
-//   P-hat, dS' = P-hat (dP descaled - delta k8s), tile amax over the 64 x 128 tile (all 256 threads), psi by the F2 / F2b
-//   rules, codes P-hat8 = e4m3(P-hat), dS'8 = e4m3(dS' / psi) written to two swizzled K-major tiles [key][row]
+//   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each into one of two (S | dP) tensor-memory buffers, issued
+//                                  as soon as that buffer has been read, i.e. up to two m-blocks ahead
+//   compute warps                  P-hat, dS' = P-hat (dP descaled - delta k8s), tile amax over the 64 x 128 tile (one named
+//                                  barrier among the 256 compute threads), psi by the F2 / F2b rules, codes
+//                                  P-hat8 = e4m3(P-hat), dS'8 = e4m3(dS' / psi) into two swizzled K-major tiles [key][row];
+//                                  the dS' codes also go straight to the global workspace tile (32 bytes per thread)
 //   dV_tmp (+)= P-hat8^T dO8       M128 N128 K32 x 2, zero-initialised on the first m-block of a 128-row dO scale block
 //   dK_tmp  = dS'8^T Q8            M128 N128 K32 x 2, zero-initialised
-//   dK += dK_tmp * (psi 2^-8 q8sc)  and, once per 128-row block,  dV += dV_tmp * (2^-8 do8sc)    in registers
+//   dK += dK_tmp * (psi 2^-8 q8sc)  and, once per 128-row block,  dV += dV_tmp * (2^-8 do8sc)   in registers, one m-block
+//                                  late, so the products complete under the next m-block's arithmetic
 // Q8 / dO8 m-block tiles serve twice: K-major as the B operand of S^T / dP^T and MN-major as the B operand of dK / dV.
-// The finished 128 x 128 dS' tile ([key][row], the layout pass 2 reads as an MN-major A operand) leaves by a TMA store.
+// The dS' tile layout in global memory is [key][row] (128 x 128 bytes), which pass 2 reads as an MN-major A operand.
 #include "dm_attn_common.cuh"
 #include "dm_host.h"
 
@@ -25,18 +31,20 @@ namespace {
 constexpr int kTile = 128 * 128;
 constexpr int kHalf = 64 * 128;
 constexpr int kStages = 4;
+constexpr int kComputeThreads = 256;
+constexpr int kThreads = 384;          // two compute warpgroups + one issuer warpgroup (only its first warp works)
 
 struct Bwd1Smem {
     alignas(1024) uint8_t k[kTile];
     alignas(1024) uint8_t v[kTile];
     alignas(1024) uint8_t q[kStages][kHalf];
     alignas(1024) uint8_t dO[kStages][kHalf];
-    alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]
+    alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]; an m-block owns one 64-byte half
     alignas(1024) uint8_t ds[kTile];      // dS' codes, same layout
-    float rc[2][64];                      // 8 - lse * log2e per row of the m-block
-    float dlk[2][2][64];                  // delta * k8s(group) per row
+    float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
+    float dlk[3][2][64];                  // delta * k8s(group) per row
     float amax[2][8];
-    uint64_t bar_kv, bar_qdo[kStages], bar_sp[2], bar_dkv;
+    uint64_t bar_kv, bar_qdo[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full, bar_dkv_free;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -50,21 +58,18 @@ struct Bwd1Params {
     const float* delta;
     __nv_bfloat16* dk;
     __nv_bfloat16* dv;
+    uint8_t* ds_ws;
     float* psi;
     int H, Hk, N, h0, hcount, causal;
     int* status;
 };
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                 const __grid_constant__ CUtensorMap tm_ds, const Bwd1Params p) {
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const Bwd1Params p) {
     extern __shared__ uint8_t smem_raw[];
     Bwd1Smem& s = *reinterpret_cast<Bwd1Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = warp >> 2;                      // column half: rows [32 g, 32 g + 32) of S^T, d [64 g, 64 g + 64) of dK / dV
-    const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
-    const int kgrp = key >> 6;                    // 64-key scale group inside the block
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
     const int nbn = p.N / 128, nbm = p.N / 64;
@@ -77,9 +82,13 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         s.abort_flag = 0;
         dm::mbar_init(&s.bar_kv, 1);
         for (int i = 0; i < kStages; ++i) dm::mbar_init(&s.bar_qdo[i], 1);
-        dm::mbar_init(&s.bar_sp[0], 1);
-        dm::mbar_init(&s.bar_sp[1], 1);
-        dm::mbar_init(&s.bar_dkv, 1);
+        for (int i = 0; i < 2; ++i) {
+            dm::mbar_init(&s.bar_sp_full[i], 1);
+            dm::mbar_init(&s.bar_sp_free[i], 8);
+            dm::mbar_init(&s.bar_codes[i], 8);
+        }
+        dm::mbar_init(&s.bar_dkv_full, 1);
+        dm::mbar_init(&s.bar_dkv_free, 8);
         dm::fence_mbar_init();
     }
     if (warp == 0) dm::tmem_alloc(&s.tmem_base, 512);
@@ -88,207 +97,222 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     dm::tc_fence_after();
     const uint32_t tmem = s.tmem_base;
     const uint32_t t_dv = tmem + 256, t_dk = tmem + 384;
-    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
-    const int q_row0 = hc.bh * p.N;
-    const int kv_row0 = hc.bhk * p.N + J * 128;
-    constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
-    constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
 
-    auto load_qdo = [&](int it) {
-        const int st = it % kStages, mb = m_lo + it;
-        dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kHalf);
-        dm::tma_load_2d(s.q[st], &tm_q, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
-        dm::tma_load_2d(s.dO[st], &tm_do, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
-    };
-    auto issue_sp = [&](int it) {   // S^T and dP^T of iteration `it` into buffer it & 1
-        const int st = it % kStages;
-        dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
-        dm::tc_fence_after();
-        const uint32_t ka = dm::smem_u32(s.k), va = dm::smem_u32(s.v), qa = dm::smem_u32(s.q[st]), da = dm::smem_u32(s.dO[st]);
-        const uint32_t t_s = tmem + (it & 1) * 128, t_dp = t_s + 64;
+    if (warp >= 8) {
+        // =============================================================== issuer warpgroup: TMA + tcgen05.mma, one lane
+        dm::reg_dec<40>();
+        if (warp == 8 && lane == 0) {
+            const int q_row0 = hc.bh * p.N;
+            const int kv_row0 = hc.bhk * p.N + J * 128;
+            constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
+            constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
+            const uint64_t kd = dm::smem_desc_sw128(dm::smem_u32(s.k)), vd = dm::smem_desc_sw128(dm::smem_u32(s.v));
+            const uint64_t ptd = dm::smem_desc_sw128(dm::smem_u32(s.pt)), dsd = dm::smem_desc_sw128(dm::smem_u32(s.ds));
+            auto load_qdo = [&](int it) {
+                const int st = it % kStages, mb = m_lo + it;
+                dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kHalf);
+                dm::tma_load_2d(s.q[st], &tm_q, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
+                dm::tma_load_2d(s.dO[st], &tm_do, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
+            };
+            // descriptor low words advance by bytes >> 4: 32 bytes of K = 2, 4096 bytes (32 rows) = 256, 64 bytes = 4
+            auto issue_sp = [&](int it) {
+                const int st = it % kStages, b = it & 1;
+                if (it >= 2) dm::mbar_wait(&s.bar_sp_free[b], ((it - 2) >> 1) & 1, wc);
+                dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
+                dm::tc_fence_after();
+                const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st]));
+                const uint32_t t_s = tmem + b * 128, t_dp = t_s + 64;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            dm::umma_e4m3(t_s, dm::smem_desc_sw128(ka + 32 * k), dm::smem_desc_sw128(qa + 32 * k), idesc_sp, k > 0);
+                for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_s, kd + 2 * k, qd + 2 * k, idesc_sp, k > 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            dm::umma_e4m3(t_dp, dm::smem_desc_sw128(va + 32 * k), dm::smem_desc_sw128(da + 32 * k), idesc_sp, k > 0);
-        dm::umma_commit(&s.bar_sp[it & 1]);
-    };
-
-    if (tid == 0) {
-        dm::mbar_expect_tx(&s.bar_kv, 2 * kTile);
-        dm::tma_load_2d(s.k, &tm_k, 0, kv_row0, &s.bar_kv);
-        dm::tma_load_2d(s.v, &tm_v, 0, kv_row0, &s.bar_kv);
-        for (int i = 0; i < kStages && i < n_it; ++i) load_qdo(i);
-        dm::mbar_wait(&s.bar_kv, 0, wc);
-        issue_sp(0);
-    }
-
-    const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
-    const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
-    float g_max = 0.f;
-    float dk_acc[64], dv_acc[64];
+                for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_dp, vd + 2 * k, dd + 2 * k, idesc_sp, k > 0);
+                dm::umma_commit(&s.bar_sp_full[b]);
+            };
+            auto issue_dkv = [&](int it) {
+                const int st = it % kStages, par = (m_lo + it) & 1;
+                dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
+                if (it >= 1) dm::mbar_wait(&s.bar_dkv_free, (it - 1) & 1, wc);
+                dm::tc_fence_after();
+                const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st]));
 #pragma unroll
-    for (int i = 0; i < 64; ++i) { dk_acc[i] = 0.f; dv_acc[i] = 0.f; }
-
-    // Per-row constants of an m-block (8 - lse * log2e, delta * k8s(group)) are fetched one m-block ahead into registers by
-    // threads 0..127 (row = tid & 63, scale group = tid >> 6) and parked in shared memory at the end of the iteration.
-    const int rc_r = tid & 63, rc_grp = (tid >> 6) & 1;
-    const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + rc_grp];
-    auto fetch_rows = [&](int it, float& lse_v, float& dl_v) {
-        if (tid < 128) {
-            const int64_t gi = (int64_t)hc.bh * p.N + (int64_t)(m_lo + it) * 64 + rc_r;
-            lse_v = p.lse[gi];
-            dl_v = p.delta[gi];
+                for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dv, ptd + 4 * par + 2 * k, dd + 256 * k, idesc_dkv, (par != 0) || k > 0);
+#pragma unroll
+                for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dk, dsd + 4 * par + 2 * k, qd + 256 * k, idesc_dkv, k > 0);
+                dm::umma_commit(&s.bar_dkv_full);
+            };
+            dm::mbar_expect_tx(&s.bar_kv, 2 * kTile);
+            dm::tma_load_2d(s.k, &tm_k, 0, kv_row0, &s.bar_kv);
+            dm::tma_load_2d(s.v, &tm_v, 0, kv_row0, &s.bar_kv);
+            for (int i = 0; i < kStages && i < n_it; ++i) load_qdo(i);
+            dm::mbar_wait(&s.bar_kv, 0, wc);
+            issue_sp(0);
+            if (n_it > 1) issue_sp(1);
+            for (int it = 0; it < n_it; ++it) {
+                issue_dkv(it);
+                if (it + 2 < n_it) issue_sp(it + 2);
+                // the Q / dO stage of m-block it - 1 is free once its dK / dV products have completed; the compute warps
+                // have waited for exactly that before they released the product buffers for m-block `it`
+                if (it >= 1 && it - 1 + kStages < n_it) load_qdo(it - 1 + kStages);
+            }
+            // the last products: wait so shared memory stays valid until the tensor pipe has read it
+            dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
         }
-    };
-    auto park_rows = [&](int it, float lse_v, float dl_v) {
-        if (tid < 128) {
-            s.dlk[it & 1][rc_grp][rc_r] = dl_v * rc_kk;
-            if (rc_grp == 0) s.rc[it & 1][rc_r] = dm::phat_row_const(lse_v);
-        }
-    };
-    {
-        float a = 0.f, b = 0.f;
-        fetch_rows(0, a, b);
-        park_rows(0, a, b);
-    }
-    float q8sc_n = p.q8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
-    float do8sc_n = p.do8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
-    float g_prev = 0.f, f_prev = 0.f;
-    __syncthreads();
-
-    // Folds the dK_tmp (and, on the second m-block of a dO scale block, dV_tmp) products of iteration `it` into the register
-    // accumulators; called one iteration late so the MMAs have completed under the next m-block's arithmetic.
-    auto fold = [&](int it, float g_fold, float f_fold) {
-        dm::mbar_wait(&s.bar_dkv, it & 1, wc);
-        dm::tc_fence_after();
-        if (tid == 0 && it + kStages < n_it) load_qdo(it + kStages);   // that iteration's Q / dO stage is free
-        float t[64];
-        dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-        dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
-        dm::tmem_ld_wait();
+    } else {
+        // =============================================================== compute warps
+        dm::reg_inc<232>();
+        const int g = warp >> 2;                      // column half: rows [32 g, 32 g + 32) of S^T, d [64 g, 64 g + 64) of dK / dV
+        const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
+        const int kgrp = key >> 6;                    // 64-key scale group inside the block
+        const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+        const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
+        const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
+        float g_max = 0.f;
+        float dk_acc[64], dv_acc[64];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_fold, dk_acc[i]);
-        if (((m_lo + it) & 1) == 1) {
-            dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-            dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
+        for (int i = 0; i < 64; ++i) { dk_acc[i] = 0.f; dv_acc[i] = 0.f; }
+
+        // Per-row constants (8 - lse * log2e, delta * k8s(group)) travel two m-blocks ahead: fetched into registers by
+        // threads 0..127 (row = tid & 63, scale group = tid >> 6), parked in a 3-deep shared-memory ring after the amax
+        // barrier of the current m-block; the amax barrier of the next m-block orders the ring for its readers.
+        const int rc_r = tid & 63, rc_grp = (tid >> 6) & 1;
+        const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + rc_grp];
+        auto fetch_rows = [&](int it, float& lse_v, float& dl_v) {
+            if (tid < 128 && it < n_it) {
+                const int64_t gi = (int64_t)hc.bh * p.N + (int64_t)(m_lo + it) * 64 + rc_r;
+                lse_v = p.lse[gi];
+                dl_v = p.delta[gi];
+            }
+        };
+        auto park_rows = [&](int it, float lse_v, float dl_v) {
+            if (tid < 128 && it < n_it) {
+                s.dlk[it % 3][rc_grp][rc_r] = dl_v * rc_kk;
+                if (rc_grp == 0) s.rc[it % 3][rc_r] = dm::phat_row_const(lse_v);
+            }
+        };
+        float lse_n = 0.f, dl_n = 0.f;
+        fetch_rows(0, lse_n, dl_n);
+        park_rows(0, lse_n, dl_n);
+        fetch_rows(1, lse_n, dl_n);
+        park_rows(1, lse_n, dl_n);
+        fetch_rows(2, lse_n, dl_n);                    // parked during iteration 0
+        float q8sc_n = p.q8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
+        float do8sc_n = p.do8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
+        float g_prev = 0.f, f_prev = 0.f;
+        dm::named_bar_sync(1, kComputeThreads);
+
+        auto fold = [&](int it, float g_fold, float f_fold) {
+            dm::mbar_wait(&s.bar_dkv_full, it & 1, wc);
+            dm::tc_fence_after();
+            float t[64];
+            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
+            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
             dm::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 64; ++i) dv_acc[i] = fmaf(t[i], f_fold, dv_acc[i]);
-        }
-    };
-
-    for (int it = 0; it < n_it; ++it) {
-        const int mb = m_lo + it, st = it % kStages, par = mb & 1, sb = it & 1;
-        if (tid == 0 && it + 1 < n_it) issue_sp(it + 1);
-        float lse_n = 0.f, dl_n = 0.f;
-        if (it + 1 < n_it) fetch_rows(it + 1, lse_n, dl_n);
-        const float q8sc = q8sc_n, do8sc = do8sc_n;
-        if (it + 1 < n_it) {
-            q8sc_n = p.q8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
-            do8sc_n = p.do8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
-        }
-        const float dsc = dm::descale_log2(q8sc, k8s_t);
-        const float dpk = do8sc * v8s_t * k8s_t;
-        dm::mbar_wait(&s.bar_sp[sb], (it >> 1) & 1, wc);
-        dm::tc_fence_after();
-
-        // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory
-        float sv[32], ds[32];
-        dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
-        dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128 + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
-        dm::tmem_ld_wait();
-        const bool diag = p.causal && (mb >> 1) == J;
-        const int row_in_pair = par * 64 + g * 32;         // row offset of column 0 inside the 128-row pair
-        float amax = 0.f;
+            for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_fold, dk_acc[i]);
+            if (((m_lo + it) & 1) == 1) {
+                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
+                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
+                dm::tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            float ph = dm::phat(sv[c], dsc, s.rc[sb][g * 32 + c]);
-            if (diag && key > row_in_pair + c) ph = 0.f;
-            sv[c] = ph;
-            ds[c] = ph * (ds[c] * dpk - s.dlk[sb][kgrp][g * 32 + c]);
-            amax = fmaxf(amax, fabsf(ds[c]));
-        }
-        {
-            uint32_t w[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) w[c] = dm::cvt_e4m3x4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
-            *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        if (lane == 0) s.amax[sb][warp] = amax;
-        if (tid == 0 && par == 0) dm::tma_store_wait_read0();   // the previous pair's dS' tile has left shared memory
-        dm::tc_fence_before();
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[sb][i]);
-        const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
-        const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
-        const float psi = fmaxf(psi_raw, g_max * (256.0f * 1e-8f) / q8sc);
-        const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
-        const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
-        g_max = fmaxf(g_max, g_cur);
-        if (tid == 0) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
-
-        // ---- phase 2: dS' codes
-        {
-            uint32_t w[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
-            *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
-        }
-        dm::fence_proxy_async_smem();
-        // ---- the previous m-block's products, complete by now, go into the accumulators
-        if (it > 0) fold(it - 1, g_prev, f_prev);
-        g_prev = g_cur;
-        f_prev = dm::kMoInv * do8sc;
-        if (it + 1 < n_it) park_rows(it + 1, lse_n, dl_n);
-        dm::tc_fence_before();
-        __syncthreads();
-
-        if (tid == 0) {
-            dm::tc_fence_after();
-            const uint32_t pa = dm::smem_u32(s.pt) + par * 64, sa = dm::smem_u32(s.ds) + par * 64;
-            const uint32_t qa = dm::smem_u32(s.q[st]), da = dm::smem_u32(s.dO[st]);
-#pragma unroll
-            for (int k = 0; k < 2; ++k)
-                dm::umma_e4m3(t_dv, dm::smem_desc_sw128(pa + 32 * k), dm::smem_desc_sw128(da + 4096 * k), idesc_dkv, (par != 0) || k > 0);
-#pragma unroll
-            for (int k = 0; k < 2; ++k)
-                dm::umma_e4m3(t_dk, dm::smem_desc_sw128(sa + 32 * k), dm::smem_desc_sw128(qa + 4096 * k), idesc_dkv, k > 0);
-            dm::umma_commit(&s.bar_dkv);
-            if (par == 1) {   // the 128 x 128 dS' tile of this row pair is complete
-                dm::tma_store_2d(&tm_ds, 0, (int)((((int64_t)bhl * nbn + (mb >> 1)) * nbn + J) * 128), s.ds);
-                dm::tma_store_commit();
+                for (int i = 0; i < 64; ++i) dv_acc[i] = fmaf(t[i], f_fold, dv_acc[i]);
             }
-        }
-    }
-    fold(n_it - 1, g_prev, f_prev);
-    dm::tc_fence_before();
+            dm::tc_fence_before();
+            dm::mbar_arrive_warp(&s.bar_dkv_free);
+        };
 
-    // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
-    if (tid == 0) dm::tma_store_wait_all0();
-    const float ik = 1.0f / k8s_t;
-    const int n_glob = J * 128 + key;
-    const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 128 + g * 64;
+        for (int it = 0; it < n_it; ++it) {
+            const int mb = m_lo + it, par = mb & 1, sb = it & 1, rb = it % 3;
+            const float q8sc = q8sc_n, do8sc = do8sc_n;
+            if (it + 1 < n_it) {
+                q8sc_n = p.q8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
+                do8sc_n = p.do8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
+            }
+            const float dsc = dm::descale_log2(q8sc, k8s_t);
+            const float dpk = do8sc * v8s_t * k8s_t;
+            dm::mbar_wait(&s.bar_sp_full[sb], (it >> 1) & 1, wc);
+            dm::tc_fence_after();
+
+            // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory
+            float sv[32], ds[32];
+            dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
+            dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128 + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
+            dm::tmem_ld_wait();
+            dm::tc_fence_before();
+            dm::mbar_arrive_warp(&s.bar_sp_free[sb]);      // this (S | dP) buffer may be overwritten
+            const bool diag = p.causal && (mb >> 1) == J;
+            const int row_in_pair = par * 64 + g * 32;     // row offset of column 0 inside the 128-row pair
+            float amax = 0.f;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        uint32_t wk[4], wv[4];
+            for (int c = 0; c < 32; ++c) {
+                float ph = dm::phat(sv[c], dsc, s.rc[rb][g * 32 + c]);
+                if (diag && key > row_in_pair + c) ph = 0.f;
+                sv[c] = ph;
+                ds[c] = ph * (ds[c] * dpk - s.dlk[rb][kgrp][g * 32 + c]);
+                amax = fmaxf(amax, fabsf(ds[c]));
+            }
+            {
+                uint32_t w[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[8 * c + 2 * e] * ik, dk_acc[8 * c + 2 * e + 1] * ik);
-            __nv_bfloat162 b = __floats2bfloat162_rn(dv_acc[8 * c + 2 * e], dv_acc[8 * c + 2 * e + 1]);
-            wk[e] = *reinterpret_cast<uint32_t*>(&a);
-            wv[e] = *reinterpret_cast<uint32_t*>(&b);
+                for (int c = 0; c < 8; ++c) w[c] = dm::cvt_e4m3x4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
+                *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            if (lane == 0) s.amax[sb][warp] = amax;
+            dm::named_bar_sync(1, kComputeThreads);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[sb][i]);
+            park_rows(it + 2, lse_n, dl_n);
+            fetch_rows(it + 3, lse_n, dl_n);
+            const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
+            const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
+            const float psi = fmaxf(psi_raw, g_max * (256.0f * 1e-8f) / q8sc);
+            const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
+            const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
+            g_max = fmaxf(g_max, g_cur);
+            if (tid == 0) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
+
+            // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
+            {
+                uint32_t w[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
+                *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+                uint4* gp = reinterpret_cast<uint4*>(p.ds_ws + ((((int64_t)bhl * nbn + (mb >> 1)) * nbn + J) * 128 + key) * 128 + row_in_pair);
+                gp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                gp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+            dm::fence_proxy_async_smem();
+            dm::mbar_arrive_warp(&s.bar_codes[sb]);
+            // ---- the previous m-block's products, complete by now, go into the accumulators
+            if (it > 0) fold(it - 1, g_prev, f_prev);
+            g_prev = g_cur;
+            f_prev = dm::kMoInv * do8sc;
         }
-        reinterpret_cast<uint4*>(p.dk + off)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
-        reinterpret_cast<uint4*>(p.dv + off)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        fold(n_it - 1, g_prev, f_prev);
+
+        // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
+        const float ik = 1.0f / k8s_t;
+        const int n_glob = J * 128 + key;
+        const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 128 + g * 64;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t wk[4], wv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[8 * c + 2 * e] * ik, dk_acc[8 * c + 2 * e + 1] * ik);
+                __nv_bfloat162 b = __floats2bfloat162_rn(dv_acc[8 * c + 2 * e], dv_acc[8 * c + 2 * e + 1]);
+                wk[e] = *reinterpret_cast<uint32_t*>(&a);
+                wv[e] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            reinterpret_cast<uint4*>(p.dk + off)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+            reinterpret_cast<uint4*>(p.dv + off)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
     }
+    dm::tc_fence_before();
     __syncthreads();
     if (warp == 0) dm::tmem_dealloc(tmem, 512);
 }
@@ -317,19 +341,18 @@ extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, 
     const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
     DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads (got %llu tiles)",
                (unsigned long long)ntiles);
-    CUtensorMap tq, td, tk, tv, ts;
+    CUtensorMap tq, td, tk, tv;
     if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&td, do8, 128, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&ts, ds8_ws, 128, ntiles * 128, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
-    Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), psi_ws,
+    Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
                  sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
     const int smem = (int)sizeof(Bwd1Smem) + 1024;
     DM_CUDA(cudaFuncSetAttribute(bwd1_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    bwd1_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
+    bwd1_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
