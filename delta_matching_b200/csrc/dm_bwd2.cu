@@ -7,7 +7,8 @@
 // too, so no transposed copy of anything exists.  Per key tile: 4 x tcgen05.mma (M128 N128 K32) into one of two
 // tensor-memory buffers, zero-initialised; then each thread (row, 64 d columns) folds dq += psi(row's m-block, tile) *
 // tmp unless the tile is a pass-1 zero tile (psi == 0) or sits more than 8 decades below the row block's running psi
-// max (the F2 / F2b skip rules).  Tiles stream through a 3-stage TMA ring; the pass is bound by the dS' read from HBM.
+// max (the F2 / F2b skip rules).  Tiles stream through a 3-stage TMA ring; the pass is bound by the dS' read from HBM, so two CTAs share an SM (256 tensor-
+// memory columns, 96 KB shared memory, <= 128 registers each) to keep more loads in flight.
 #include "dm_attn_common.cuh"
 #include "dm_host.h"
 
@@ -36,7 +37,7 @@ struct Bwd2Params {
     int* status;
 };
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_k, const Bwd2Params p) {
     extern __shared__ uint8_t smem_raw[];
     Bwd2Smem& s = *reinterpret_cast<Bwd2Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -104,12 +105,14 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
         dm::tc_fence_after();
         if (tid == 0 && it + kStages < n_it) load(it + kStages);   // the MMA that read this stage is complete
         if (take) {                                                // warp-uniform: a warp's 32 rows share one m-block
-            float t[64];
-            dm::tmem_ld32(dm::tmem_addr(tmem + (it & 1) * 128, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-            dm::tmem_ld32(dm::tmem_addr(tmem + (it & 1) * 128, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
-            dm::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 64; ++i) dq[i] = fmaf(t[i], psi_cur, dq[i]);
+            for (int h = 0; h < 2; ++h) {
+                float t[32];
+                dm::tmem_ld32(dm::tmem_addr(tmem + (it & 1) * 128, lane_base, g * 64 + 32 * h), reinterpret_cast<uint32_t*>(t));
+                dm::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dq[32 * h + i] = fmaf(t[i], psi_cur, dq[32 * h + i]);
+            }
             psi_max = fmaxf(psi_max, psi_cur);
         }
         dm::tc_fence_before();

@@ -2,11 +2,13 @@
 // P-hat * dP, built from the backward's own fp8 operands with exactly the P-hat arithmetic pass 1 uses, so that
 // rowsum(P-hat * (dP - delta)) cancels to fp32 round-off (csrc/fp11_delta_v6.h:338-376,458-462 of the reference).
 //
-// One CTA = 128 query rows of one (batch, head); 256 threads; key tiles of 128 keys ascending.  Per tile
-//   S  = Q  K^T   and   dP = dO V^T      8 x tcgen05.mma into one of two tensor-memory buffers (S | dP, 256 columns)
-// while the threads reduce the other buffer: thread (row, key group g) forms P-hat for its 64 keys, accumulates
-// fma(P-hat, dP * (do8sc * v8sc), a) per 32-key half in ascending key order, and folds each half's fp32 partial
-// (times 2^-8) into an fp64 accumulator.  The two key groups' fp64 sums are added at the end and rounded once.
+// One CTA = 128 query rows of one (batch, head); 256 threads; key tiles of 128 keys ascending; TWO CTAs per SM (256
+// tensor-memory columns, < 113 KB shared memory and <= 128 registers each), so one CTA's MMAs run under the other's
+// arithmetic.  Per tile
+//   S  = Q  K^T   and   dP = dO V^T      8 x tcgen05.mma into tensor memory (S | dP, 256 columns)
+// then thread (row, key group g) forms P-hat for its 64 keys, accumulates fma(P-hat, dP * (do8sc * v8sc), a) per 32-key
+// half in ascending key order, and folds each half's fp32 partial (times 2^-8) into an fp64 accumulator.  The two key
+// groups' fp64 sums are added at the end and rounded once.
 // Also the debug row-sum kernel: the same loop with delta subtracted, producing rowsum and abs-rowsum of
 // P-hat * (dP - delta) / 256.
 #include "dm_attn_common.cuh"
@@ -46,7 +48,7 @@ struct DeltaParams {
 };
 
 template <bool kDebug>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DeltaParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -69,7 +71,7 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         dm::fence_mbar_init();
     }
-    if (warp == 0) dm::tmem_alloc(&s.tmem_base, 512);
+    if (warp == 0) dm::tmem_alloc(&s.tmem_base, 256);
     dm::tc_fence_before();
     __syncthreads();
     dm::tc_fence_after();
@@ -85,19 +87,19 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         dm::tma_load_2d(s.k[st], &tm_k, 0, kv_row0 + it * 128, &s.bar_kv[st]);
         dm::tma_load_2d(s.v[st], &tm_v, 0, kv_row0 + it * 128, &s.bar_kv[st]);
     };
-    auto issue = [&](int it) {   // S and dP of key tile `it` into buffer it & 1
+    auto issue = [&](int it) {   // S and dP of key tile `it`
         const int st = it & 1;
         dm::mbar_wait(&s.bar_kv[st], (it >> 1) & 1, wc);
         dm::tc_fence_after();
         const uint32_t qa = dm::smem_u32(s.q), da = dm::smem_u32(s.dO), ka = dm::smem_u32(s.k[st]), va = dm::smem_u32(s.v[st]);
-        const uint32_t t_s = tmem + st * 256, t_dp = t_s + 128;
+        const uint32_t t_s = tmem, t_dp = t_s + 128;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
             dm::umma_e4m3(t_s, dm::smem_desc_sw128(qa + 32 * k), dm::smem_desc_sw128(ka + 32 * k), idesc, k > 0);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
             dm::umma_e4m3(t_dp, dm::smem_desc_sw128(da + 32 * k), dm::smem_desc_sw128(va + 32 * k), idesc, k > 0);
-        dm::umma_commit(&s.bar_mma[st]);
+        dm::umma_commit(&s.bar_mma[0]);
     };
 
     if (tid == 0) {
@@ -119,15 +121,14 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it & 1;
-        if (tid == 0 && it + 1 < n_tiles) issue(it + 1);
         const float ks = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * it + g];
         const float vs = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * it + g];
         const float dsc = dm::descale_log2(q8sc, ks);
         const float dpsc = do8sc * vs;
         const bool diag = p.causal && it == I;
-        dm::mbar_wait(&s.bar_mma[st], (it >> 1) & 1, wc);
+        dm::mbar_wait(&s.bar_mma[0], it & 1, wc);
         dm::tc_fence_after();
-        const uint32_t t_s = tmem + st * 256, t_dp = t_s + 128;
+        const uint32_t t_s = tmem, t_dp = t_s + 128;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             float sv[32], dp[32];
@@ -151,8 +152,11 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (kDebug) acc_abs += (double)(aa * dm::kMoInv);
         }
         dm::tc_fence_before();
-        __syncthreads();                       // both buffers' readers are done; stage `st` tiles are free
-        if (tid == 0 && it + 2 < n_tiles) load_kv(it + 2);
+        __syncthreads();                       // S | dP have been read; stage `st` tiles are free
+        if (tid == 0) {
+            if (it + 1 < n_tiles) issue(it + 1);
+            if (it + 2 < n_tiles) load_kv(it + 2);
+        }
     }
 
     s.part[g][row] = acc;
@@ -162,7 +166,7 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         p.out[(int64_t)hc.bh * p.N + n_glob] = (float)(s.part[0][row] + s.part[1][row]);
         if (kDebug) p.out_abs[(int64_t)hc.bh * p.N + n_glob] = (float)(s.part_abs[0][row] + s.part_abs[1][row]);
     }
-    if (warp == 0) dm::tmem_dealloc(tmem, 512);
+    if (warp == 0) dm::tmem_dealloc(tmem, 256);
 }
 
 template <bool kDebug>
