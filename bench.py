@@ -217,7 +217,8 @@ def main():
     # count the library's kernel launches per call (one entry point can launch more than one kernel)
     launches = {"n": 0}
     per_call = {"dm_kmean": 2, "dm_quant": 1, "dm_quant_do": 1, "dm_fwd_fp8": 1, "dm_delta_fp8": 1, "dm_bwd_fp8_pass1": 1,
-                "dm_bwd_fp8_pass2": 1, "dm_gqa_fold": 1}
+                "dm_bwd_fp8_pass2": 1, "dm_gqa_fold": 1, "dm_attn_forward": 6,
+                "dm_attn_backward": 3 + (1 if mode == "matched" else 0) + (2 if Hk < H else 0)}
     orig_call = _lib._call
 
     def counting_call(name, *a):
@@ -332,6 +333,9 @@ def main():
                 return r
             for _ in range(reps):
                 flush.fill_(1)
+                # keep the GPU busy (~2 ms) while the host enqueues the whole chain, so that the events bracket kernel time
+                # only and not the gaps in which the GPU would wait for the host
+                torch.cuda._sleep(4_000_000)
                 Q8, Q8s = timed("quant_q", lambda: _lib.quant(0, qf))
                 km = timed("kmean", lambda: _lib.kmean(kf))
                 K8, K8s = timed("quant_k", lambda: _lib.quant(1, kf, km))

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "dm_bwd_fp8_pass1": (C.c_int, [_P] * 10 + [DmShape, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, *_ERR]),
     "dm_bwd_fp8_pass2": (C.c_int, [_P] * 3 + [DmShape, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_gqa_fold": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_attn_forward": (C.c_int, [_P, DmStrides, _P, DmStrides, _P, DmStrides, DmShape] + [_P] * 10 + [_P, *_ERR]),
+    "dm_attn_backward": (C.c_int, [_P, DmStrides, _P, DmStrides] + [_P] * 7 + [DmShape, C.c_int32] + [_P] * 10 + [_P, *_ERR]),
     "dm_bwd_dbg_rowsum": (C.c_int, [_P] * 10 + [DmShape, _P, _P, _P, *_ERR]),
     "dm_probe_mma": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
     "dm_device_status": (C.c_int, [C.POINTER(C.c_int32), *_ERR]),
@@ -257,6 +259,50 @@ def gqa_fold(x_bnhd, Hk):
         out = torch.empty(B, N, Hk, D, device=x_bnhd.device, dtype=torch.bfloat16)
         _call("dm_gqa_fold", _ptr(x_bnhd), B, N, H, Hk, D, _ptr(out), _stream(x_bnhd.device))
     return out
+
+
+def attn_forward(q, k, v, causal):
+    """Quantizers + forward in one library call.  q (B, N, H, D), k / v (B, N, Hk, D) bf16 views (unit head_dim stride).
+    Returns O, LSE, Q8, Q8s, K8, K8s, V8, V8s."""
+    B, N, H, D = q.shape
+    Hk = k.shape[2]
+    q, k, v = _unit_lane(q), _unit_lane(k), _unit_lane(v)
+    dev = q.device
+    rq, rk = blocks(D)
+    f32, bf = torch.float32, torch.bfloat16
+    with torch.cuda.device(dev):
+        e = lambda shape, dt: torch.empty(shape, device=dev, dtype=dt)
+        Q8, K8, V8 = e((B * H, N, D), E4M3), e((B * Hk, N, D), E4M3), e((B * Hk, N, D), E4M3)
+        Q8s, K8s, V8s = e((B * H, N // rq), f32), e((B * Hk, N // rk), f32), e((B * Hk, N // rk), f32)
+        km, part = e((B * Hk, D), f32), e((B * Hk * (N // 64) * D,), f32)
+        O, lse = e((B, N, H, D), bf), e((B * H, N), f32)
+        _call("dm_attn_forward", _ptr(q), _strides_bnhd(q), _ptr(k), _strides_bnhd(k), _ptr(v), _strides_bnhd(v),
+              _shape(B, H, Hk, N, D, causal), _ptr(Q8), _ptr(Q8s), _ptr(K8), _ptr(K8s), _ptr(V8), _ptr(V8s), _ptr(km), _ptr(part),
+              _ptr(O), _ptr(lse), _stream(dev))
+    return O, lse, Q8, Q8s, K8, K8s, V8, V8s
+
+
+def attn_backward(dO, O, lse, Q8, Q8s, K8, K8s, V8, V8s, B, H, Hk, causal, matched):
+    """dO quantizer + pass 0 / 1 / 2 + GQA fold for all heads in one library call.  Returns dq (B, N, H, D), dk / dv
+    (B, N, Hk, D) bf16."""
+    BH, N, D = Q8.shape
+    dO = _unit_lane(dO)
+    dev = Q8.device
+    f32, bf = torch.float32, torch.bfloat16
+    with torch.cuda.device(dev):
+        e = lambda shape, dt: torch.empty(shape, device=dev, dtype=dt)
+        dO8, dO8s, delta = e((BH, N, D), E4M3), e((BH, N // blocks(D)[0]), f32), e((BH, N), f32)
+        nb_ds, nb_psi = bwd_workspace_bytes(B, H, Hk, N, D, causal, H)
+        ws_ds, ws_psi = e((nb_ds,), torch.uint8), e((nb_psi // 4,), f32)
+        dq = e((B, N, H, D), bf)
+        dk, dv = e((B, N, Hk, D), bf), e((B, N, Hk, D), bf)
+        dkh = e((B, N, H, D), bf) if Hk < H else None
+        dvh = e((B, N, H, D), bf) if Hk < H else None
+        os_ = _strides_bnhd(O) if not matched else DmStrides(0, 0, 0)
+        _call("dm_attn_backward", _ptr(dO), _strides_bnhd(dO), _ptr(O) if not matched else C.c_void_p(0), os_, _ptr(Q8), _ptr(K8),
+              _ptr(V8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(lse), _shape(B, H, Hk, N, D, causal), 1 if matched else 0, _ptr(dO8),
+              _ptr(dO8s), _ptr(delta), _ptr(dkh), _ptr(dvh), _ptr(ws_ds), _ptr(ws_psi), _ptr(dq), _ptr(dk), _ptr(dv), _stream(dev))
+    return dq, dk, dv
 
 
 def bwd_dbg_rowsum(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal):

@@ -18,8 +18,8 @@ class _DMAttn(torch.autograd.Function):
     def forward(ctx, q, k, v, causal, delta_mode):
         B, H, N, D = q.shape
         Hk = k.shape[1]
-        Q8, Q8s, K8, K8s, V8, V8s = ops.quant_qkv(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
-        O, Lse = ops.fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal)
+        fwd = ops.attn_fwd if torch.compiler.is_compiling() else ops.attn_fwd_eager
+        O, Lse, Q8, Q8s, K8, K8s, V8, V8s = fwd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal)
         ctx.save_for_backward(Q8, Q8s, K8, K8s, V8, V8s, O, Lse)
         ctx.dims = (B, H, Hk, N, D)
         ctx.causal = causal
@@ -33,12 +33,8 @@ class _DMAttn(torch.autograd.Function):
         Q8, Q8s, K8, K8s, V8, V8s, O, Lse = ctx.saved_tensors
         if dO.stride(-1) != 1:          # e.g. the expanded gradient of o.sum(): the quantizer reads rows with a unit lane stride
             dO = dO.contiguous()
-        stale = ctx.delta_mode != "matched"
-        dO8, dO8s, Dlt = ops.quant_do(dO, O if stale else None)
-        dq, dk, dv = ops.bwd_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, Lse, Dlt if stale else None, B, H, Hk, ctx.causal)
-        if Hk < H:
-            dk = ops.gqa_fold(dk, Hk)
-            dv = ops.gqa_fold(dv, Hk)
+        bwd = ops.attn_bwd if torch.compiler.is_compiling() else ops.attn_bwd_eager
+        dq, dk, dv = bwd(dO, O, Lse, Q8, Q8s, K8, K8s, V8, V8s, B, H, Hk, ctx.causal, ctx.delta_mode == "matched")
         return dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3), None, None
 
 

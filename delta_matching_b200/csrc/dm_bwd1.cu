@@ -351,7 +351,15 @@ extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, 
     Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
                  sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
     const int smem = (int)sizeof(Bwd1Smem) + 1024;
-    DM_CUDA(cudaFuncSetAttribute(bwd1_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    {
+        static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
+        int dev = 0;
+        DM_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            DM_CUDA(cudaFuncSetAttribute(bwd1_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
     bwd1_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;

@@ -156,7 +156,15 @@ extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const v
     const float sm = sh.D == 128 ? 0.08838834764831845f : 0.0625f;
     Bwd2Params p{psi_ws, static_cast<__nv_bfloat16*>(dq), sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, sm / 256.0f, status};
     const int smem = (int)sizeof(Bwd2Smem) + 1024;
-    DM_CUDA(cudaFuncSetAttribute(bwd2_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    {
+        static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
+        int dev = 0;
+        DM_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            DM_CUDA(cudaFuncSetAttribute(bwd2_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
     bwd2_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;

@@ -179,7 +179,15 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
     if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     const int smem = (int)sizeof(DeltaSmem) + 1024;
-    DM_CUDA(cudaFuncSetAttribute(delta_d128_kernel<kDebug>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    {
+        static bool attr_done[64] = {false};      // per template instance; the attribute is per device and sticky
+        int dev = 0;
+        DM_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            DM_CUDA(cudaFuncSetAttribute(delta_d128_kernel<kDebug>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
     delta_d128_kernel<kDebug><<<dim3(sh.N / 128, sh.B * p.hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;

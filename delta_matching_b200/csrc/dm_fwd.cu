@@ -268,7 +268,15 @@ extern "C" int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const 
     if (!status) return DM_ERR_CUDA;
     FwdParams p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
     const int smem = (int)sizeof(FwdSmem) + 1024;
-    DM_CUDA(cudaFuncSetAttribute(fwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    {
+        static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
+        int dev = 0;
+        DM_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+            DM_CUDA(cudaFuncSetAttribute(fwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        }
+    }
     fwd_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;

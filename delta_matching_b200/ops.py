@@ -108,3 +108,55 @@ def gqa_fold(x: Tensor, Hk: int) -> Tensor:
 def _(x, Hk):
     B, N, H, D = x.shape
     return x.new_empty((B, N, Hk, D))
+
+
+def attn_fwd_eager(q: Tensor, k: Tensor, v: Tensor, causal: bool):
+    """The whole forward as plain calls into the library: q (B, N, H, D), k / v (B, N, Hk, D) bf16 ->
+    O, LSE, Q8, Q8s, K8, K8s, V8, V8s.  The autograd route calls this directly in eager mode (the torch.library dispatcher
+    costs more host time per call than all the kernel launches together) and the custom op below under torch.compile."""
+    return _lib.attn_forward(q, k, v, causal)
+
+
+@torch.library.custom_op("dm_b200::attn_fwd", mutates_args=())
+def attn_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """attn_fwd_eager as one traceable op."""
+    return attn_fwd_eager(q, k, v, causal)
+
+
+@attn_fwd.register_fake
+def _(q, k, v, causal):
+    B, N, H, D = q.shape
+    Hk = k.shape[2]
+    rq, rk = _lib.blocks(D)
+    f = lambda *s, dt: q.new_empty(s, dtype=dt)
+    return (f(B, N, H, D, dt=torch.bfloat16), f(B * H, N, dt=torch.float32), f(B * H, N, D, dt=E4M3), f(B * H, N // rq, dt=torch.float32),
+            f(B * Hk, N, D, dt=E4M3), f(B * Hk, N // rk, dt=torch.float32), f(B * Hk, N, D, dt=E4M3), f(B * Hk, N // rk, dt=torch.float32))
+
+
+def attn_bwd_eager(dO: Tensor, O: Tensor, lse: Tensor, Q8: Tensor, Q8s: Tensor, K8: Tensor, K8s: Tensor, V8: Tensor, V8s: Tensor,
+                   B: int, H: int, Hk: int, causal: bool, matched: bool):
+    """The whole backward as plain calls into the library: dO quantizer (with the stale delta only in the stale mode),
+    pass 0 / 1 / 2 with the head-group split, GQA fold.  Returns dQ (B, N, H, D), dK / dV (B, N, Hk, D) bf16."""
+    from .split import backward_all_heads, _bwd_heads_per_call
+    if _bwd_heads_per_call(B, H, Hk, H // Hk, Q8.shape[1]) >= H:      # no head-group split: one library call
+        return _lib.attn_backward(dO, O, lse, Q8, Q8s, K8, K8s, V8, V8s, B, H, Hk, causal, matched)
+    with torch.cuda.device(dO.device):
+        dO8, dO8s, delta = _lib.quant_do(dO, None if matched else O)
+        dq, dk, dv = backward_all_heads(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal)
+        if Hk < H:
+            dk, dv = _lib.gqa_fold(dk, Hk), _lib.gqa_fold(dv, Hk)
+    return dq, dk, dv
+
+
+@torch.library.custom_op("dm_b200::attn_bwd", mutates_args=())
+def attn_bwd(dO: Tensor, O: Tensor, lse: Tensor, Q8: Tensor, Q8s: Tensor, K8: Tensor, K8s: Tensor, V8: Tensor, V8s: Tensor, B: int,
+             H: int, Hk: int, causal: bool, matched: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """attn_bwd_eager as one traceable op."""
+    return attn_bwd_eager(dO, O, lse, Q8, Q8s, K8, K8s, V8, V8s, B, H, Hk, causal, matched)
+
+
+@attn_bwd.register_fake
+def _(dO, O, lse, Q8, Q8s, K8, K8s, V8, V8s, B, H, Hk, causal, matched):
+    BH, N, D = Q8.shape
+    return (Q8.new_empty((B, N, H, D), dtype=torch.bfloat16), Q8.new_empty((B, N, Hk, D), dtype=torch.bfloat16),
+            Q8.new_empty((B, N, Hk, D), dtype=torch.bfloat16))

@@ -112,6 +112,23 @@ int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const void* k8, Dm
 int dm_gqa_fold(const void* x_bf16, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, void* out_bf16, void* stream,
                 char* err, size_t errlen);
 
+/* The whole forward in one call: Q / K / V quantizers (with the K mean) and the forward kernel, on the caller's stream and
+ * in the caller's buffers (code and scale tensors are outputs the backward needs; km [B*Hk, D] and km_partials
+ * (dm_kmean_scratch_bytes) are scratch).  Replaces the op sequence of _DMAttn._forward (delta_matching/attn.py:52-68). */
+int dm_attn_forward(const void* q_bf16, DmStrides qs, const void* k_bf16, DmStrides ks, const void* v_bf16, DmStrides vs, DmShape s,
+                    void* q8, float* q8s, void* k8, float* k8s, void* v8, float* v8s, float* km, float* km_partials, void* o_bf16,
+                    float* lse, void* stream, char* err, size_t errlen);
+
+/* The whole backward for all heads in one call: dO quantizer (stale delta from `o_bf16` when matched == 0), pass 0 when
+ * matched != 0, pass 1, pass 2 and, with GQA, the fold of dK / dV to KV heads.  do8 / do8s / delta / ds8_ws / psi_ws and,
+ * with GQA, dk_heads / dv_heads (B, N, H, D) are caller-provided intermediates; results dq (B, N, H, D), dk / dv
+ * (B, N, Hk, D) bf16.  Replaces the op sequence of _DMAttn._backward without the head-group split
+ * (delta_matching/attn.py:76-118); callers that need the split drive pass 0 / 1 / 2 per head range themselves. */
+int dm_attn_backward(const void* do_bf16, DmStrides dos, const void* o_bf16, DmStrides os, const void* q8, const void* k8,
+                     const void* v8, const float* q8s, const float* k8s, const float* v8s, const float* lse, DmShape s,
+                     int32_t matched, void* do8, float* do8s, float* delta, void* dk_heads, void* dv_heads, void* ds8_ws,
+                     float* psi_ws, void* dq_bf16, void* dk_bf16, void* dv_bf16, void* stream, char* err, size_t errlen);
+
 /* Debug: row sums and absolute row sums of P-hat * (dP - delta) / 256 over all visible keys, fp32 [B*H, N] each, from
  * the same operands and arithmetic as pass 1.  Replaces the DM_DBG ops bwd_fp8_dbg / delta_fp8_dbg
  * (csrc/delta_matching_api.cpp:612-680). */
