@@ -249,6 +249,11 @@ int check_shape(const DmShape& s, int h0, int hcount, char* err, size_t errlen) 
 }
 }  // namespace dmh
 
+namespace dmh {
+int launch_fwd_d256(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s, DmShape sh,
+                    int h0, int hcount, void* o, float* lse, void* stream, char* err, size_t errlen);
+}
+
 extern "C" int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
                           DmShape sh, int32_t h0, int32_t hcount, void* o, float* lse, void* stream, char* err, size_t errlen) {
     int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
@@ -259,7 +264,7 @@ extern "C" int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const 
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     DM_REQUIRE(dmh::aligned16(q8) && dmh::aligned16(k8) && dmh::aligned16(v8) && dmh::aligned16(o), DM_ERR_ARG,
                "code and output pointers must be 16-byte aligned");
-    DM_REQUIRE(sh.D == 128, DM_ERR_UNSUPPORTED, "the forward kernel for head_dim %d is not built yet (head_dim 128 only)", sh.D);
+    if (sh.D == 256) return dmh::launch_fwd_d256(q8, k8, v8, q8s, k8s, v8s, sh, h0, hcount, o, lse, stream, err, errlen);
     CUtensorMap tq, tk, tv;
     if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
