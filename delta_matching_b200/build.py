@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdm_b200.so")
 OBJ = os.path.join(HERE, "build")
-SOURCES = ["dm_host.cu", "dm_quant.cu", "dm_probe.cu", "dm_fwd.cu", "dm_delta.cu", "dm_bwd1.cu", "dm_bwd2.cu", "dm_compose.cu", "dm_fwd256.cu", "dm_bwd1_256.cu", "dm_bwd2_256.cu"]
+SOURCES = ["dm_host.cu", "dm_quant.cu", "dm_probe.cu", "dm_fwd.cu", "dm_delta.cu", "dm_bwd1.cu", "dm_bwd2.cu", "dm_compose.cu", "dm_fwd256.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v", "--expt-relaxed-constexpr"]
 

@@ -30,19 +30,33 @@ namespace {
 
 constexpr int kTile = 128 * 128;
 constexpr int kHalf = 64 * 128;
-constexpr int kStages = 4;
 constexpr int kComputeThreads = 256;
 constexpr int kThreads = 384;          // two compute warpgroups + one issuer warpgroup (only its first warp works)
 
+// Geometry per head dim.  head_dim 256 (csrc/mainloop_bwd_sm90_fp8v10.hpp:1674-1761 of the reference): a code row is two
+// 128-byte sub-tiles, K / V scales per 32 keys, Q / dO scales per 64-row m-block, psi per 64 rows x 64 keys (so a CTA's 128
+// keys carry two psi tiles per m-block, one per lane half), dV folded every m-block.  The dK / dV accumulators of 128 keys x
+// 256 columns do not fit the registers, so two CTAs (blockIdx.z = d half) share a key block: both form S^T / dP^T, each
+// keeps its 128 columns of dK / dV, and only d half 0 writes the dS' tiles and psi.
+template <int kD>
+struct Geo {
+    static constexpr int kDH = kD / 128;                 // 128-byte sub-tiles per code row
+    static constexpr int kStages = kD == 128 ? 4 : 3;    // Q / dO ring depth
+    static constexpr int kKeysPerScale = kD == 128 ? 64 : 32;
+    static constexpr int kGrp = 128 / kKeysPerScale;     // K / V scale groups per key block
+};
+
+template <int kD>
 struct Bwd1Smem {
-    alignas(1024) uint8_t k[kTile];
-    alignas(1024) uint8_t v[kTile];
-    alignas(1024) uint8_t q[kStages][kHalf];
-    alignas(1024) uint8_t dO[kStages][kHalf];
+    static constexpr int kDH = Geo<kD>::kDH, kStages = Geo<kD>::kStages, kGrp = Geo<kD>::kGrp;
+    alignas(1024) uint8_t k[kDH][kTile];
+    alignas(1024) uint8_t v[kDH][kTile];
+    alignas(1024) uint8_t q[kStages][kDH][kHalf];
+    alignas(1024) uint8_t dO[kStages][kDH][kHalf];
     alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]; an m-block owns one 64-byte half
     alignas(1024) uint8_t ds[kTile];      // dS' codes, same layout
     float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
-    float dlk[3][2][64];                  // delta * k8s(group) per row
+    float dlk[3][kGrp][64];               // delta * k8s(group) per row
     float amax[2][8];
     uint64_t bar_kv, bar_qdo[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full, bar_dkv_free;
     uint32_t tmem_base;
@@ -64,11 +78,15 @@ struct Bwd1Params {
     int* status;
 };
 
+template <int kD>
 __global__ void __launch_bounds__(kThreads, 1)
-bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const Bwd1Params p) {
     extern __shared__ uint8_t smem_raw[];
-    Bwd1Smem& s = *reinterpret_cast<Bwd1Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using G = Geo<kD>;
+    constexpr int kDH = G::kDH, kStages = G::kStages, kGrp = G::kGrp, kKPS = G::kKeysPerScale;
+    const int zh = blockIdx.z;                    // d half whose dK / dV columns this CTA keeps (always 0 at head_dim 128)
+    Bwd1Smem<kD>& s = *reinterpret_cast<Bwd1Smem<kD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
@@ -106,13 +124,14 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const int kv_row0 = hc.bhk * p.N + J * 128;
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
-            const uint64_t kd = dm::smem_desc_sw128(dm::smem_u32(s.k)), vd = dm::smem_desc_sw128(dm::smem_u32(s.v));
             const uint64_t ptd = dm::smem_desc_sw128(dm::smem_u32(s.pt)), dsd = dm::smem_desc_sw128(dm::smem_u32(s.ds));
             auto load_qdo = [&](int it) {
                 const int st = it % kStages, mb = m_lo + it;
-                dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kHalf);
-                dm::tma_load_2d(s.q[st], &tm_q, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
-                dm::tma_load_2d(s.dO[st], &tm_do, 0, q_row0 + mb * 64, &s.bar_qdo[st]);
+                dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
+                for (int hh = 0; hh < kDH; ++hh) {
+                    dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + mb * 64, &s.bar_qdo[st]);
+                    dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + mb * 64, &s.bar_qdo[st]);
+                }
             };
             // descriptor low words advance by bytes >> 4: 32 bytes of K = 2, 4096 bytes (32 rows) = 256, 64 bytes = 4
             auto issue_sp = [&](int it) {
@@ -120,12 +139,19 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (it >= 2) dm::mbar_wait(&s.bar_sp_free[b], ((it - 2) >> 1) & 1, wc);
                 dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
                 dm::tc_fence_after();
-                const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st]));
                 const uint32_t t_s = tmem + b * 128, t_dp = t_s + 64;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_s, kd + 2 * k, qd + 2 * k, idesc_sp, k > 0);
+                for (int hh = 0; hh < kDH; ++hh) {
+                    const uint64_t kd = dm::smem_desc_sw128(dm::smem_u32(s.k[hh])), qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st][hh]));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_dp, vd + 2 * k, dd + 2 * k, idesc_sp, k > 0);
+                    for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_s, kd + 2 * k, qd + 2 * k, idesc_sp, (hh | k) != 0);
+                }
+#pragma unroll
+                for (int hh = 0; hh < kDH; ++hh) {
+                    const uint64_t vd = dm::smem_desc_sw128(dm::smem_u32(s.v[hh])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st][hh]));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_dp, vd + 2 * k, dd + 2 * k, idesc_sp, (hh | k) != 0);
+                }
                 dm::umma_commit(&s.bar_sp_full[b]);
             };
             auto issue_dkv = [&](int it) {
@@ -133,26 +159,29 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
                 if (it >= 1) dm::mbar_wait(&s.bar_dkv_free, (it - 1) & 1, wc);
                 dm::tc_fence_after();
-                const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st]));
+                const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st][zh])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st][zh]));
+                // head_dim 128: dV_tmp accumulates the two m-blocks of a 128-row dO scale block; head_dim 256: one m-block
 #pragma unroll
-                for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dv, ptd + 4 * par + 2 * k, dd + 256 * k, idesc_dkv, (par != 0) || k > 0);
+                for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dv, ptd + 4 * par + 2 * k, dd + 256 * k, idesc_dkv, (kD == 128 && par != 0) || k > 0);
 #pragma unroll
                 for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dk, dsd + 4 * par + 2 * k, qd + 256 * k, idesc_dkv, k > 0);
                 dm::umma_commit(&s.bar_dkv_full);
             };
-            dm::mbar_expect_tx(&s.bar_kv, 2 * kTile);
-            dm::tma_load_2d(s.k, &tm_k, 0, kv_row0, &s.bar_kv);
-            dm::tma_load_2d(s.v, &tm_v, 0, kv_row0, &s.bar_kv);
+            dm::mbar_expect_tx(&s.bar_kv, 2 * kDH * kTile);
+            for (int hh = 0; hh < kDH; ++hh) {
+                dm::tma_load_2d(s.k[hh], &tm_k, 128 * hh, kv_row0, &s.bar_kv);
+                dm::tma_load_2d(s.v[hh], &tm_v, 128 * hh, kv_row0, &s.bar_kv);
+            }
             for (int i = 0; i < kStages && i < n_it; ++i) load_qdo(i);
             dm::mbar_wait(&s.bar_kv, 0, wc);
             issue_sp(0);
             if (n_it > 1) issue_sp(1);
             for (int it = 0; it < n_it; ++it) {
                 issue_dkv(it);
-                if (it + 2 < n_it) issue_sp(it + 2);
                 // the Q / dO stage of m-block it - 1 is free once its dK / dV products have completed; the compute warps
                 // have waited for exactly that before they released the product buffers for m-block `it`
                 if (it >= 1 && it - 1 + kStages < n_it) load_qdo(it - 1 + kStages);
+                if (it + 2 < n_it) issue_sp(it + 2);
             }
             // the last products: wait so shared memory stays valid until the tensor pipe has read it
             dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
@@ -162,10 +191,13 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         dm::reg_inc<232>();
         const int g = warp >> 2;                      // column half: rows [32 g, 32 g + 32) of S^T, d [64 g, 64 g + 64) of dK / dV
         const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
-        const int kgrp = key >> 6;                    // 64-key scale group inside the block
+        const int kgrp = key / kKPS;                  // K / V scale group inside the block
+        const int khalf = key >> 6;                   // 64-key half (the psi tile at head_dim 256)
+        const int nsq = kD == 128 ? nbn : nbm;        // Q / dO scale blocks per head
+        auto sq_idx = [&](int mb_) { return kD == 128 ? (mb_ >> 1) : mb_; };
         const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
-        const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
-        const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + kgrp];
+        const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
+        const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         float g_max = 0.f;
         float dk_acc[64], dv_acc[64];
 #pragma unroll
@@ -174,17 +206,17 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // Per-row constants (8 - lse * log2e, delta * k8s(group)) travel two m-blocks ahead: fetched into registers by
         // threads 0..127 (row = tid & 63, scale group = tid >> 6), parked in a 3-deep shared-memory ring after the amax
         // barrier of the current m-block; the amax barrier of the next m-block orders the ring for its readers.
-        const int rc_r = tid & 63, rc_grp = (tid >> 6) & 1;
-        const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * J + rc_grp];
+        const int rc_r = tid & 63, rc_grp = (tid >> 6) & (kGrp - 1);
+        const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + rc_grp];
         auto fetch_rows = [&](int it, float& lse_v, float& dl_v) {
-            if (tid < 128 && it < n_it) {
+            if (tid < 64 * kGrp && it < n_it) {
                 const int64_t gi = (int64_t)hc.bh * p.N + (int64_t)(m_lo + it) * 64 + rc_r;
                 lse_v = p.lse[gi];
                 dl_v = p.delta[gi];
             }
         };
         auto park_rows = [&](int it, float lse_v, float dl_v) {
-            if (tid < 128 && it < n_it) {
+            if (tid < 64 * kGrp && it < n_it) {
                 s.dlk[it % 3][rc_grp][rc_r] = dl_v * rc_kk;
                 if (rc_grp == 0) s.rc[it % 3][rc_r] = dm::phat_row_const(lse_v);
             }
@@ -195,8 +227,8 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         fetch_rows(1, lse_n, dl_n);
         park_rows(1, lse_n, dl_n);
         fetch_rows(2, lse_n, dl_n);                    // parked during iteration 0
-        float q8sc_n = p.q8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
-        float do8sc_n = p.do8s[(int64_t)hc.bh * nbn + (m_lo >> 1)];
+        float q8sc_n = p.q8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)];
+        float do8sc_n = p.do8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)];
         float g_prev = 0.f, f_prev = 0.f;
         dm::named_bar_sync(1, kComputeThreads);
 
@@ -209,7 +241,7 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             dm::tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_fold, dk_acc[i]);
-            if (((m_lo + it) & 1) == 1) {
+            if (kD == 256 || ((m_lo + it) & 1) == 1) {
                 dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
                 dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
                 dm::tmem_ld_wait();
@@ -224,8 +256,8 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const int mb = m_lo + it, par = mb & 1, sb = it & 1, rb = it % 3;
             const float q8sc = q8sc_n, do8sc = do8sc_n;
             if (it + 1 < n_it) {
-                q8sc_n = p.q8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
-                do8sc_n = p.do8s[(int64_t)hc.bh * nbn + ((mb + 1) >> 1)];
+                q8sc_n = p.q8s[(int64_t)hc.bh * nsq + sq_idx(mb + 1)];
+                do8sc_n = p.do8s[(int64_t)hc.bh * nsq + sq_idx(mb + 1)];
             }
             const float dsc = dm::descale_log2(q8sc, k8s_t);
             const float dpk = do8sc * v8s_t * k8s_t;
@@ -261,8 +293,13 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             if (lane == 0) s.amax[sb][warp] = amax;
             dm::named_bar_sync(1, kComputeThreads);
+            if (kD == 128) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[sb][i]);
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[sb][i]);
+            } else {                                   // psi tile = this thread's 64-key half: warps 2h, 2h+1 of both warpgroups
+                const int w0 = 2 * khalf;
+                amax = fmaxf(fmaxf(s.amax[sb][w0], s.amax[sb][w0 + 1]), fmaxf(s.amax[sb][w0 + 4], s.amax[sb][w0 + 5]));
+            }
             park_rows(it + 2, lse_n, dl_n);
             fetch_rows(it + 3, lse_n, dl_n);
             const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
@@ -271,7 +308,13 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
             const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
             g_max = fmaxf(g_max, g_cur);
-            if (tid == 0) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
+            if (zh == 0) {
+                if (kD == 128) {
+                    if (tid == 0) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
+                } else if (tid == 0 || tid == 64) {    // one writer per 64-key half: psi [heads, N/64, N/64]
+                    p.psi[((int64_t)bhl * nbm + mb) * nbm + 2 * J + khalf] = tile_zero ? 0.f : psi;
+                }
+            }
 
             // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
             {
@@ -281,9 +324,11 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
                 *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
-                uint4* gp = reinterpret_cast<uint4*>(p.ds_ws + ((((int64_t)bhl * nbn + (mb >> 1)) * nbn + J) * 128 + key) * 128 + row_in_pair);
-                gp[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                gp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                if (zh == 0) {
+                    uint4* gp = reinterpret_cast<uint4*>(p.ds_ws + ((((int64_t)bhl * nbn + (mb >> 1)) * nbn + J) * 128 + key) * 128 + row_in_pair);
+                    gp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    gp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                }
             }
             dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[sb]);
@@ -297,7 +342,7 @@ bwd1_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
         const float ik = 1.0f / k8s_t;
         const int n_glob = J * 128 + key;
-        const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 128 + g * 64;
+        const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128 + g * 64;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             uint32_t wk[4], wv[4];
@@ -337,30 +382,39 @@ extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, 
     for (int i = 0; i < 14; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     DM_REQUIRE(dmh::aligned16(dk) && dmh::aligned16(dv) && dmh::aligned16(ds8_ws), DM_ERR_ARG, "outputs and workspace must be 16-byte aligned");
-    DM_REQUIRE(sh.D == 128, DM_ERR_UNSUPPORTED, "backward pass 1 for head_dim %d is not built yet (head_dim 128 only)", sh.D);
     const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
     DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads (got %llu tiles)",
                (unsigned long long)ntiles);
     CUtensorMap tq, td, tk, tv;
-    if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&td, do8, 128, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&tv, v8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tq, q8, sh.D, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&td, do8, sh.D, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tk, k8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tv, v8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
                  sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
-    const int smem = (int)sizeof(Bwd1Smem) + 1024;
-    {
-        static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
+    if (sh.D == 128) {
+        const int smem = (int)sizeof(Bwd1Smem<128>) + 1024;
+        static bool done[64] = {false};
         int dev = 0;
         DM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(bwd1_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+        if (dev < 0 || dev >= 64 || !done[dev]) {
+            DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) done[dev] = true;
         }
+        bwd1_kernel<128><<<dim3(sh.N / 128, sh.B * hcount, 1), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
+    } else {
+        const int smem = (int)sizeof(Bwd1Smem<256>) + 1024;
+        static bool done[64] = {false};
+        int dev = 0;
+        DM_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !done[dev]) {
+            DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) done[dev] = true;
+        }
+        bwd1_kernel<256><<<dim3(sh.N / 128, sh.B * hcount, 2), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     }
-    bwd1_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

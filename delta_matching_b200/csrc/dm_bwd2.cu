@@ -134,6 +134,125 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     if (warp == 0) dm::tmem_dealloc(tmem, 256);
 }
 
+// ---- head_dim 256 ---------------------------------------------------------------------------------------------------------
+// psi is per 64 rows x 64 keys (csrc/fq8_dq_pass2.h:95-125,188 of the reference), so a 128-key tile is two reductions (keys
+// 0..63 and 64..127: two K steps each) times two d halves = four M128 N128 accumulators = all 512 tensor-memory columns;
+// a thread (row, d half) folds the two key halves in ascending order with its row's psi and the F2 / F2b skip rules.
+struct Bwd2Smem256 {
+    alignas(1024) uint8_t a[kStages][kTile];      // dS' tile [key][row]
+    alignas(1024) uint8_t b[kStages][2][kTile];   // K8 tile [d half][key][128 bytes]
+    uint64_t bar_ld[kStages], bar_mma;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(256, 1)
+bwd2_d256_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_k, const Bwd2Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    Bwd2Smem256& s = *reinterpret_cast<Bwd2Smem256*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;                           // d half
+    const int row = (warp & 3) * 32 + lane;
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const int bhl = hc.b * p.hcount + (hc.h - p.h0);
+    const int nbn = p.N / 128, nbm = p.N / 64;
+    const int rb = nbn - 1 - (int)blockIdx.x;
+    const int n_it = p.causal ? rb + 1 : nbn;
+    dm::WaitCtx wc{&s.abort_flag, p.status};
+
+    if (tid == 0) {
+        s.abort_flag = 0;
+        for (int i = 0; i < kStages; ++i) dm::mbar_init(&s.bar_ld[i], 1);
+        dm::mbar_init(&s.bar_mma, 1);
+        dm::fence_mbar_init();
+    }
+    if (warp == 0) dm::tmem_alloc(&s.tmem_base, 512);
+    dm::tc_fence_before();
+    __syncthreads();
+    dm::tc_fence_after();
+    const uint32_t tmem = s.tmem_base;
+    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+    const int64_t tile0 = ((int64_t)bhl * nbn + rb) * nbn;
+    const int kv_row0 = hc.bhk * p.N;
+    constexpr uint32_t idesc = dm::idesc_e4m3(128, 128, true, true);
+
+    auto load = [&](int it) {
+        const int st = it % kStages;
+        dm::mbar_expect_tx(&s.bar_ld[st], 3 * kTile);
+        dm::tma_load_2d(s.a[st], &tm_ds, 0, (int)((tile0 + it) * 128), &s.bar_ld[st]);
+        dm::tma_load_2d(s.b[st][0], &tm_k, 0, kv_row0 + it * 128, &s.bar_ld[st]);
+        dm::tma_load_2d(s.b[st][1], &tm_k, 128, kv_row0 + it * 128, &s.bar_ld[st]);
+    };
+    auto issue = [&](int it) {
+        const int st = it % kStages;
+        dm::mbar_wait(&s.bar_ld[st], (it / kStages) & 1, wc);
+        dm::tc_fence_after();
+        const uint64_t ad = dm::smem_desc_sw128(dm::smem_u32(s.a[st]));
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+            for (int dh = 0; dh < 2; ++dh) {
+                const uint64_t bd = dm::smem_desc_sw128(dm::smem_u32(s.b[st][dh]));
+#pragma unroll
+                for (int k2 = 0; k2 < 2; ++k2)
+                    dm::umma_e4m3(tmem + kh * 256 + dh * 128, ad + 256 * (2 * kh + k2), bd + 256 * (2 * kh + k2), idesc, k2 > 0);
+            }
+        dm::umma_commit(&s.bar_mma);
+    };
+    if (tid == 0) {
+        for (int i = 0; i < kStages && i < n_it; ++i) load(i);
+        issue(0);
+    }
+
+    const int mb = 2 * rb + (row >> 6);
+    const float* psi_row = p.psi + ((int64_t)bhl * nbm + mb) * nbm;     // [heads, N/64, N/64]
+    float psi_max = 0.f;
+    float dq[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) dq[i] = 0.f;
+
+    for (int it = 0; it < n_it; ++it) {
+        const float psi2[2] = {psi_row[2 * it], psi_row[2 * it + 1]};
+        dm::mbar_wait(&s.bar_mma, it & 1, wc);
+        dm::tc_fence_after();
+        if (tid == 0 && it + kStages < n_it) load(it + kStages);
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+            const float psi_cur = psi2[kh];
+            const bool take = (psi_cur != 0.f) && !(psi_cur < psi_max * 1e-8f);
+            if (take) {                                            // warp-uniform
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    float t[32];
+                    dm::tmem_ld32(dm::tmem_addr(tmem + kh * 256 + g * 128, lane_base, 32 * h), reinterpret_cast<uint32_t*>(t));
+                    dm::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) dq[32 * h + i] = fmaf(t[i], psi_cur, dq[32 * h + i]);
+                }
+                psi_max = fmaxf(psi_max, psi_cur);
+            }
+        }
+        dm::tc_fence_before();
+        __syncthreads();
+        if (tid == 0 && it + 1 < n_it) issue(it + 1);
+    }
+
+    const int n_glob = rb * 128 + row;
+    __nv_bfloat16* op = p.dq + (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 256 + g * 128;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+        uint32_t w4[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(dq[8 * c + 2 * e] * p.final_scale, dq[8 * c + 2 * e + 1] * p.final_scale);
+            w4[e] = *reinterpret_cast<uint32_t*>(&t);
+        }
+        reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    }
+    __syncthreads();
+    if (warp == 0) dm::tmem_dealloc(tmem, 512);
+}
+
 }  // namespace
 
 extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape sh, int32_t h0, int32_t hcount,
@@ -145,16 +264,22 @@ extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const v
     for (int i = 0; i < 4; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     DM_REQUIRE(dmh::aligned16(dq), DM_ERR_ARG, "dq must be 16-byte aligned");
-    DM_REQUIRE(sh.D == 128, DM_ERR_UNSUPPORTED, "backward pass 2 for head_dim %d is not built yet (head_dim 128 only)", sh.D);
     const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
     DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads");
     CUtensorMap ts, tk;
     if ((rc = dmh::make_tmap_u8(&ts, ds8_ws, 128, ntiles * 128, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tk, k8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     const float sm = sh.D == 128 ? 0.08838834764831845f : 0.0625f;
     Bwd2Params p{psi_ws, static_cast<__nv_bfloat16*>(dq), sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, sm / 256.0f, status};
+    if (sh.D == 256) {
+        const int smem = (int)sizeof(Bwd2Smem256) + 1024;
+        DM_CUDA(cudaFuncSetAttribute(bwd2_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        bwd2_d256_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
+        DM_CUDA(cudaGetLastError());
+        return DM_OK;
+    }
     const int smem = (int)sizeof(Bwd2Smem) + 1024;
     {
         static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device

@@ -22,11 +22,15 @@ namespace {
 
 constexpr int kTile = 128 * 128;
 
+// kD = 256: a code row is two 128-byte sub-tiles (8 MMA K steps), K / V scales per 32 keys (exactly the 32-key halves this
+// kernel already reduces separately), Q / dO scales per 64 rows; 192 KB of shared memory, so one CTA per SM.
+template <int kD>
 struct DeltaSmem {
-    alignas(1024) uint8_t q[kTile];
-    alignas(1024) uint8_t dO[kTile];
-    alignas(1024) uint8_t k[2][kTile];
-    alignas(1024) uint8_t v[2][kTile];
+    static constexpr int kDH = kD / 128;
+    alignas(1024) uint8_t q[kDH][kTile];
+    alignas(1024) uint8_t dO[kDH][kTile];
+    alignas(1024) uint8_t k[2][kDH][kTile];
+    alignas(1024) uint8_t v[2][kDH][kTile];
     double part[2][128];
     double part_abs[2][128];
     uint64_t bar_qdo, bar_kv[2], bar_mma[2];
@@ -47,12 +51,13 @@ struct DeltaParams {
     int* status;
 };
 
-template <bool kDebug>
-__global__ void __launch_bounds__(256, 2)
-delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+template <bool kDebug, int kD>
+__global__ void __launch_bounds__(256, kD == 128 ? 2 : 1)
+delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DeltaParams p) {
     extern __shared__ uint8_t smem_raw[];
-    DeltaSmem& s = *reinterpret_cast<DeltaSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int kDH = kD / 128;
+    DeltaSmem<kD>& s = *reinterpret_cast<DeltaSmem<kD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
@@ -83,37 +88,47 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     auto load_kv = [&](int it) {
         const int st = it & 1;
-        dm::mbar_expect_tx(&s.bar_kv[st], 2 * kTile);
-        dm::tma_load_2d(s.k[st], &tm_k, 0, kv_row0 + it * 128, &s.bar_kv[st]);
-        dm::tma_load_2d(s.v[st], &tm_v, 0, kv_row0 + it * 128, &s.bar_kv[st]);
+        dm::mbar_expect_tx(&s.bar_kv[st], 2 * kDH * kTile);
+        for (int hh = 0; hh < kDH; ++hh) {
+            dm::tma_load_2d(s.k[st][hh], &tm_k, 128 * hh, kv_row0 + it * 128, &s.bar_kv[st]);
+            dm::tma_load_2d(s.v[st][hh], &tm_v, 128 * hh, kv_row0 + it * 128, &s.bar_kv[st]);
+        }
     };
     auto issue = [&](int it) {   // S and dP of key tile `it`
         const int st = it & 1;
         dm::mbar_wait(&s.bar_kv[st], (it >> 1) & 1, wc);
         dm::tc_fence_after();
-        const uint32_t qa = dm::smem_u32(s.q), da = dm::smem_u32(s.dO), ka = dm::smem_u32(s.k[st]), va = dm::smem_u32(s.v[st]);
         const uint32_t t_s = tmem, t_dp = t_s + 128;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            dm::umma_e4m3(t_s, dm::smem_desc_sw128(qa + 32 * k), dm::smem_desc_sw128(ka + 32 * k), idesc, k > 0);
+        for (int hh = 0; hh < kDH; ++hh) {
+            const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[hh])), kd = dm::smem_desc_sw128(dm::smem_u32(s.k[st][hh]));
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            dm::umma_e4m3(t_dp, dm::smem_desc_sw128(da + 32 * k), dm::smem_desc_sw128(va + 32 * k), idesc, k > 0);
+            for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_s, qd + 2 * k, kd + 2 * k, idesc, (hh | k) != 0);
+        }
+#pragma unroll
+        for (int hh = 0; hh < kDH; ++hh) {
+            const uint64_t dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[hh])), vd = dm::smem_desc_sw128(dm::smem_u32(s.v[st][hh]));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_dp, dd + 2 * k, vd + 2 * k, idesc, (hh | k) != 0);
+        }
         dm::umma_commit(&s.bar_mma[0]);
     };
 
     if (tid == 0) {
-        dm::mbar_expect_tx(&s.bar_qdo, 2 * kTile);
-        dm::tma_load_2d(s.q, &tm_q, 0, q_row0, &s.bar_qdo);
-        dm::tma_load_2d(s.dO, &tm_do, 0, q_row0, &s.bar_qdo);
+        dm::mbar_expect_tx(&s.bar_qdo, 2 * kDH * kTile);
+        for (int hh = 0; hh < kDH; ++hh) {
+            dm::tma_load_2d(s.q[hh], &tm_q, 128 * hh, q_row0, &s.bar_qdo);
+            dm::tma_load_2d(s.dO[hh], &tm_do, 128 * hh, q_row0, &s.bar_qdo);
+        }
         load_kv(0);
         if (n_tiles > 1) load_kv(1);
         dm::mbar_wait(&s.bar_qdo, 0, wc);
         issue(0);
     }
 
-    const float q8sc = p.q8s[(int64_t)hc.bh * nblk + I];
-    const float do8sc = p.do8s[(int64_t)hc.bh * nblk + I];
+    const int sq = kD == 128 ? (int)((int64_t)hc.bh * nblk + I) : (int)((int64_t)hc.bh * (p.N / 64) + 2 * I + (row >> 6));
+    const float q8sc = p.q8s[sq];
+    const float do8sc = p.do8s[sq];
     const int n_glob = I * 128 + row;
     const float rc = dm::phat_row_const(p.lse[(int64_t)hc.bh * p.N + n_glob]);
     const float dlt = kDebug ? p.delta_in[(int64_t)hc.bh * p.N + n_glob] : 0.f;
@@ -121,10 +136,14 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it & 1;
-        const float ks = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * it + g];
-        const float vs = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * it + g];
-        const float dsc = dm::descale_log2(q8sc, ks);
-        const float dpsc = do8sc * vs;
+        // scale group of (key group g, 32-key half h): one per 64 keys at head_dim 128, one per 32 keys at head_dim 256
+        float dsc2[2], dpsc2[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t si = kD == 128 ? (int64_t)hc.bhk * (p.N / 64) + 2 * it + g : (int64_t)hc.bhk * (p.N / 32) + 4 * it + 2 * g + h;
+            dsc2[h] = dm::descale_log2(q8sc, p.k8s[si]);
+            dpsc2[h] = do8sc * p.v8s[si];
+        }
         const bool diag = p.causal && it == I;
         dm::mbar_wait(&s.bar_mma[0], it & 1, wc);
         dm::tc_fence_after();
@@ -136,6 +155,7 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             dm::tmem_ld32(dm::tmem_addr(t_dp, lane_base, g * 64 + half * 32), reinterpret_cast<uint32_t*>(dp));
             dm::tmem_ld_wait();
             float a = 0.f, aa = 0.f;
+            const float dsc = dsc2[half], dpsc = dpsc2[half];
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 float ph = dm::phat(sv[c], dsc, rc);
@@ -169,26 +189,26 @@ delta_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (warp == 0) dm::tmem_dealloc(tmem, 256);
 }
 
-template <bool kDebug>
+template <bool kDebug, int kD>
 int launch(const void* q8, const void* k8, const void* v8, const void* do8, const DeltaParams& p, const DmShape& sh, void* stream,
            char* err, size_t errlen) {
     int rc;
     CUtensorMap tq, td, tk, tv;
-    if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&td, do8, 128, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&tv, v8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
-    const int smem = (int)sizeof(DeltaSmem) + 1024;
+    if ((rc = dmh::make_tmap_u8(&tq, q8, kD, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&td, do8, kD, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tk, k8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tv, v8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    const int smem = (int)sizeof(DeltaSmem<kD>) + 1024;
     {
         static bool attr_done[64] = {false};      // per template instance; the attribute is per device and sticky
         int dev = 0;
         DM_CUDA(cudaGetDevice(&dev));
         if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(delta_d128_kernel<kDebug>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            DM_CUDA(cudaFuncSetAttribute(delta_kernel<kDebug, kD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    delta_d128_kernel<kDebug><<<dim3(sh.N / 128, sh.B * p.hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
+    delta_kernel<kDebug, kD><<<dim3(sh.N / 128, sh.B * p.hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
@@ -204,12 +224,12 @@ extern "C" int dm_delta_fp8(const void* q8, const void* k8, const void* v8, cons
     const char* names[] = {"q8", "k8", "v8", "do8", "q8s", "k8s", "v8s", "do8s", "lse", "delta"};
     for (int i = 0; i < 10; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
-    DM_REQUIRE(sh.D == 128, DM_ERR_UNSUPPORTED, "the matched delta for head_dim %d is not built yet (head_dim 128 only)", sh.D);
     DM_REQUIRE(sh.N % 128 == 0, DM_ERR_ARG, "seqlen must be a 128-multiple (got %d)", sh.N);
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     DeltaParams p{q8s, k8s, v8s, do8s, lse, nullptr, delta, nullptr, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
-    return launch<false>(q8, k8, v8, do8, p, sh, stream, err, errlen);
+    return sh.D == 128 ? launch<false, 128>(q8, k8, v8, do8, p, sh, stream, err, errlen)
+                       : launch<false, 256>(q8, k8, v8, do8, p, sh, stream, err, errlen);
 }
 
 extern "C" int dm_bwd_dbg_rowsum(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
@@ -221,9 +241,9 @@ extern "C" int dm_bwd_dbg_rowsum(const void* q8, const void* k8, const void* v8,
     const char* names[] = {"q8", "k8", "v8", "do8", "q8s", "k8s", "v8s", "do8s", "lse", "delta", "rows", "rows_abs"};
     for (int i = 0; i < 12; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
-    DM_REQUIRE(sh.D == 128, DM_ERR_UNSUPPORTED, "the row-sum debug op for head_dim %d is not built yet", sh.D);
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     DeltaParams p{q8s, k8s, v8s, do8s, lse, delta, rows, rows_abs, sh.H, sh.Hk, sh.N, 0, sh.H, sh.causal, status};
-    return launch<true>(q8, k8, v8, do8, p, sh, stream, err, errlen);
+    return sh.D == 128 ? launch<true, 128>(q8, k8, v8, do8, p, sh, stream, err, errlen)
+                       : launch<true, 256>(q8, k8, v8, do8, p, sh, stream, err, errlen);
 }
