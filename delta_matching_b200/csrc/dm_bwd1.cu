@@ -12,7 +12,7 @@
 //   compute warps                  P-hat, dS' = P-hat (dP descaled - delta k8s), tile amax over the 64 x 128 tile (one named
 //                                  barrier among the 256 compute threads), psi by the F2 / F2b rules, codes
 //                                  P-hat8 = e4m3(P-hat), dS'8 = e4m3(dS' / psi) into two swizzled K-major tiles [key][row];
-//                                  the dS' codes also go straight to the global workspace tile (32 bytes per thread)
+//                                  the finished 128 x 128 dS' tile of a row pair leaves by one TMA store
 //   dV_tmp (+)= P-hat8^T dO8       M128 N128 K32 x 2, zero-initialised on the first m-block of a 128-row dO scale block
 //   dK_tmp  = dS'8^T Q8            M128 N128 K32 x 2, zero-initialised
 //   dK += dK_tmp * (psi 2^-8 q8sc)  and, once per 128-row block,  dV += dV_tmp * (2^-8 do8sc)   in registers, one m-block
@@ -54,9 +54,9 @@ struct Bwd1Smem {
     alignas(1024) uint8_t q[kStages][kDH][kHalf];
     alignas(1024) uint8_t dO[kStages][kDH][kHalf];
     alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]; an m-block owns one 64-byte half
-    alignas(1024) uint8_t ds[kTile];      // dS' codes, same layout
-    float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
-    float dlk[3][kGrp][64];               // delta * k8s(group) per row
+    alignas(1024) uint8_t ds[2][kTile];   // dS' codes, same layout, one tile per 128-row pair parity (a TMA store drains the other)
+    alignas(16) float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
+    alignas(16) float dlk[3][kGrp][64];               // delta * k8s(group) per row
     float amax[2][8];
     uint64_t bar_kv, bar_qdo[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full, bar_dkv_free;
     uint32_t tmem_base;
@@ -81,7 +81,8 @@ struct Bwd1Params {
 template <int kD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const Bwd1Params p) {
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_ds, const Bwd1Params p) {
     extern __shared__ uint8_t smem_raw[];
     using G = Geo<kD>;
     constexpr int kDH = G::kDH, kStages = G::kStages, kGrp = G::kGrp, kKPS = G::kKeysPerScale;
@@ -124,7 +125,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             const int kv_row0 = hc.bhk * p.N + J * 128;
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
-            const uint64_t ptd = dm::smem_desc_sw128(dm::smem_u32(s.pt)), dsd = dm::smem_desc_sw128(dm::smem_u32(s.ds));
+            const uint64_t ptd = dm::smem_desc_sw128(dm::smem_u32(s.pt));
             auto load_qdo = [&](int it) {
                 const int st = it % kStages, mb = m_lo + it;
                 dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
@@ -164,8 +165,15 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
                 for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dv, ptd + 4 * par + 2 * k, dd + 256 * k, idesc_dkv, (kD == 128 && par != 0) || k > 0);
 #pragma unroll
+                const int pp = ((m_lo + it) >> 1) & 1;                       // parity of the 128-row pair
+                const uint64_t dsd = dm::smem_desc_sw128(dm::smem_u32(s.ds[pp]));
+#pragma unroll
                 for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dk, dsd + 4 * par + 2 * k, qd + 256 * k, idesc_dkv, k > 0);
                 dm::umma_commit(&s.bar_dkv_full);
+                if (par == 1 && zh == 0) {   // the pair's 128 x 128 dS' tile is complete: one TMA store to the workspace
+                    dm::tma_store_2d(&tm_ds, 0, (int)((((int64_t)bhl * nbn + ((m_lo + it) >> 1)) * nbn + J) * 128), s.ds[pp]);
+                    dm::tma_store_commit();
+                }
             };
             dm::mbar_expect_tx(&s.bar_kv, 2 * kDH * kTile);
             for (int hh = 0; hh < kDH; ++hh) {
@@ -181,10 +189,14 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 // the Q / dO stage of m-block it - 1 is free once its dK / dV products have completed; the compute warps
                 // have waited for exactly that before they released the product buffers for m-block `it`
                 if (it >= 1 && it - 1 + kStages < n_it) load_qdo(it - 1 + kStages);
+                // m-block it + 2 may rewrite the dS' tile that a store issued two m-blocks ago is draining: S / dP of that
+                // m-block, which gate the compute warps, are issued only once the store has read shared memory
+                dm::tma_store_wait_read0();
                 if (it + 2 < n_it) issue_sp(it + 2);
             }
             // the last products: wait so shared memory stays valid until the tensor pipe has read it
             dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
+            dm::tma_store_wait_all0();
         }
     } else {
         // =============================================================== compute warps
@@ -274,14 +286,24 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             const bool diag = p.causal && (mb >> 1) == J;
             const int row_in_pair = par * 64 + g * 32;     // row offset of column 0 inside the 128-row pair
             float amax = 0.f;
+            const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 32]);
+            const float4* dl4 = reinterpret_cast<const float4*>(&s.dlk[rb][kgrp][g * 32]);
+            float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                float ph = dm::phat(sv[c], dsc, s.rc[rb][g * 32 + c]);
-                if (diag && key > row_in_pair + c) ph = 0.f;
-                sv[c] = ph;
-                ds[c] = ph * (ds[c] * dpk - s.dlk[rb][kgrp][g * 32 + c]);
-                amax = fmaxf(amax, fabsf(ds[c]));
+            for (int c4 = 0; c4 < 8; ++c4) {
+                const float4 r4 = rc4[c4], d4 = dl4[c4];
+                const float rcv[4] = {r4.x, r4.y, r4.z, r4.w}, dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = 4 * c4 + e;
+                    float ph = dm::phat(sv[c], dsc, rcv[e]);
+                    if (diag && key > row_in_pair + c) ph = 0.f;
+                    sv[c] = ph;
+                    ds[c] = ph * (ds[c] * dpk - dlv[e]);
+                    am4[e] = fmaxf(am4[e], fabsf(ds[c]));
+                }
             }
+            amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
             {
                 uint32_t w[8];
 #pragma unroll
@@ -322,13 +344,9 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
                 for (int c = 0; c < 8; ++c)
                     w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
-                *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(s.ds + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
-                if (zh == 0) {
-                    uint4* gp = reinterpret_cast<uint4*>(p.ds_ws + ((((int64_t)bhl * nbn + (mb >> 1)) * nbn + J) * 128 + key) * 128 + row_in_pair);
-                    gp[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                    gp[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                }
+                uint8_t* dst = s.ds[(mb >> 1) & 1];
+                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
             }
             dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[sb]);
@@ -385,11 +403,12 @@ extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, 
     const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
     DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads (got %llu tiles)",
                (unsigned long long)ntiles);
-    CUtensorMap tq, td, tk, tv;
+    CUtensorMap tq, td, tk, tv, ts;
     if ((rc = dmh::make_tmap_u8(&tq, q8, sh.D, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&td, do8, sh.D, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&ts, ds8_ws, 128, ntiles * 128, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
@@ -403,7 +422,7 @@ extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, 
             DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             if (dev >= 0 && dev < 64) done[dev] = true;
         }
-        bwd1_kernel<128><<<dim3(sh.N / 128, sh.B * hcount, 1), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
+        bwd1_kernel<128><<<dim3(sh.N / 128, sh.B * hcount, 1), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
     } else {
         const int smem = (int)sizeof(Bwd1Smem<256>) + 1024;
         static bool done[64] = {false};
@@ -413,7 +432,7 @@ extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, 
             DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             if (dev >= 0 && dev < 64) done[dev] = true;
         }
-        bwd1_kernel<256><<<dim3(sh.N / 128, sh.B * hcount, 2), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
+        bwd1_kernel<256><<<dim3(sh.N / 128, sh.B * hcount, 2), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
     }
     DM_CUDA(cudaGetLastError());
     return DM_OK;
