@@ -188,9 +188,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong", "cp"],
                     help="weak: every rank runs the whole config (its own seed); strong: the config's (batch x KV-head) groups "
-                         "are split across the ranks (delta_matching_b200.shard), e.g. config 5 sharded over heads")
+                         "are split across the ranks (delta_matching_b200.shard), e.g. config 5 sharded over heads; cp: the "
+                         "sequence is split across the ranks (delta_matching_b200.cp: zig-zag chunks, K / V codes round an NCCL "
+                         "ring, dK / dV partials to the key owners), head_dim 128, reported as strong scaling")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true", help="only warm-up and timed steps (for ncu captures): no e2e, no per-kernel "
                     "timing, no peak measurement, no CPU baseline")
@@ -217,7 +219,8 @@ def main():
     # count the library's kernel launches per call (one entry point can launch more than one kernel)
     launches = {"n": 0}
     per_call = {"dm_kmean": 2, "dm_quant": 1, "dm_quant_do": 1, "dm_fwd_fp8": 1, "dm_delta_fp8": 1, "dm_bwd_fp8_pass1": 1,
-                "dm_bwd_fp8_pass2": 1, "dm_gqa_fold": 1, "dm_attn_forward": 6,
+                "dm_bwd_fp8_pass2": 1, "dm_gqa_fold": 1, "dm_attn_forward": 6, "dm_kmean_partials": 1, "dm_kmean_fold": 1,
+                "dm_fold_f32": 1, "dm_fwd_fp8_cp": 1, "dm_delta_fp8_cp": 1, "dm_bwd_fp8_pass1_cp": 1, "dm_bwd_fp8_pass2_cp": 1,
                 "dm_attn_backward": 3 + (1 if mode == "matched" else 0) + (2 if Hk < H else 0)}
     orig_call = _lib._call
 
@@ -235,15 +238,24 @@ def main():
         else:
             B, Hk, H = 1, count, count * rep
         cfg = (B, N, H, Hk, D, causal, mode)          # this rank's shard; generated directly at shard size
+    cp_mode = args.scaling == "cp" and world > 1
+    cp_map = None
+    if cp_mode:
+        from delta_matching_b200 import cp as dmcp
+        cp_map = dmcp.zigzag_map(rank, world, N)      # also checks that the sequence splits
+        cfg = (B, N // world, H, Hk, D, causal, mode)  # this rank's two zig-zag chunks, generated directly at that size
+        attn = lambda a, b, c: dmcp.dm_attn_func_cp(a, b, c, causal=causal, mode=mode)
+    else:
+        attn = lambda a, b, c: dm.dm_attn_func(a, b, c, causal=causal, mode=mode)
     hq, hk, hv, hdo = make_host_inputs(cfg, 1000 + args.config + 17 * rank)
     q, k, v, dO = (t.to(dev) for t in (hq, hk, hv, hdo))
     q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
     flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
-    flops = algorithmic_flops(B, N, H, D, causal)
+    flops = algorithmic_flops(B, N, H, D, causal) / (world if cp_mode else 1)      # per rank
 
     def step():
         q.grad = k.grad = v.grad = None
-        o = dm.dm_attn_func(q, k, v, causal=causal, mode=mode)
+        o = attn(q, k, v)
         o.backward(dO)
         return o
 
@@ -290,7 +302,7 @@ def main():
     def e2e_step():
         dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
         dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
-        o = dm.dm_attn_func(dq_, dk_, dv_, causal=causal, mode=mode)
+        o = attn(dq_, dk_, dv_)
         o.backward(ddo)
         for dst, src in zip(outs, (o.detach(), dq_.grad, dk_.grad, dv_.grad)):
             dst.copy_(src, non_blocking=True)
@@ -340,14 +352,19 @@ def main():
                 km = timed("kmean", lambda: _lib.kmean(kf))
                 K8, K8s = timed("quant_k", lambda: _lib.quant(1, kf, km))
                 V8, V8s = timed("quant_v", lambda: _lib.quant(2, vf))
-                O_, lse = timed("fwd", lambda: _lib.fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal))
+                if cp_mode:        # kernel timing only: the other ranks' keys are stood in for by copies of this rank's
+                    K8, K8s, V8, V8s = (t.repeat(1, world, 1) if t.dim() == 3 else t.repeat(1, world) for t in (K8, K8s, V8, V8s))
+                O_, lse = timed("fwd", lambda: _lib.fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, cp=cp_map))
                 dO8, dO8s, dl = timed("quant_do", lambda: _lib.quant_do(dO, None if mode == "matched" else O_))
                 if mode == "matched":
-                    dl = timed("pass0_delta", lambda: _lib.delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal))
+                    dl = timed("pass0_delta", lambda: _lib.delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal,
+                                                                     cp=cp_map))
                 hp = dm.split._bwd_heads_per_call(B, H, Hk, H // Hk, N)
-                if hp >= H:
-                    dk_, dv_, ws = timed("pass1", lambda: _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, dl, B, H, Hk, causal))
-                    timed("pass2", lambda: _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal))
+                if hp >= H or cp_mode:
+                    dk_, dv_, ws = timed("pass1", lambda: _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, dl, B, H, Hk, causal,
+                                                                         cp=cp_map, out_fp32=cp_mode))
+                    timed("pass2", lambda: _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal, cp=cp_map))
+                    del dk_, dv_, ws
             torch.cuda.synchronize()
             kernels = {n: statistics.mean(a.elapsed_time(b) for a, b in ev) for n, ev in acc.items()}
         u = flops / 7.0                      # one matmul's FLOPs (causal halving already inside `flops`)
@@ -377,9 +394,13 @@ def main():
 
     if rank == 0:
         line = {"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "strong" if cp_mode else args.scaling, "vs_baseline": None,
                 "dtype": "e4m3", "data": "synthetic",
-                "config": workload_config(args.config, CONFIGS[args.config], f"dp{world} over (batch x head), no collective" +
+                "config": workload_config(args.config, CONFIGS[args.config],
+                                          f"cp{world}: sequence split in zig-zag chunks, K / V codes round an NCCL ring, dK / dV "
+                                          f"partials to the key owners" if cp_mode else
+                                          f"dp{world} over (batch x head), no collective" +
                                           ("; the config's KV groups split across ranks" if args.scaling == "strong" else
                                            "; every rank runs the whole config")),
                 "tflops_per_gpu": value / world, "frac_of_nominal_fp8_per_gpu": value / world / NOMINAL_FP8_TFLOPS,

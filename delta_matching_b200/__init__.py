@@ -21,11 +21,12 @@ import torch
 from .attn import dm_attn_func_bhnd, dm_attn_func_plain
 from . import split  # noqa: F401  (DM_BWD_* environment knobs live there)
 from .core import blocks
+from .cp import dm_attn_func_cp, zigzag_shard, zigzag_unshard
 
 __version__ = "0.1.0"
 KERNEL_NUMERICS = {"128": "Delta-Matching-128 v3", "256": "Delta-Matching-256 v1"}
-__all__ = ["dm_attn_func", "dm_attn_func_bhnd", "dm_attn_func_plain", "flash_attn_func", "blocks", "kernel_version",
-           "__version__", "KERNEL_NUMERICS"]
+__all__ = ["dm_attn_func", "dm_attn_func_bhnd", "dm_attn_func_plain", "flash_attn_func", "dm_attn_func_cp", "zigzag_shard",
+           "zigzag_unshard", "blocks", "kernel_version", "__version__", "KERNEL_NUMERICS"]
 
 
 def dm_attn_func(q, k, v, softmax_scale=None, causal=False, mode="matched"):

@@ -26,6 +26,12 @@ class DmStrides(C.Structure):
     _fields_ = [("b", C.c_int64), ("n", C.c_int64), ("h", C.c_int64)]
 
 
+class DmCp(C.Structure):
+    """Row map of a rank's Q-side tensors under a sequence split: nq local rows = half_blocks 128-row blocks starting at
+    global block off0, then the rest starting at global block off1."""
+    _fields_ = [("nq", C.c_int32), ("half_blocks", C.c_int32), ("off0", C.c_int32), ("off1", C.c_int32)]
+
+
 _ERR = (C.c_char_p, C.c_size_t)
 _P = C.c_void_p
 _SIGNATURES = {
@@ -47,6 +53,14 @@ _SIGNATURES = {
     "dm_bwd_dbg_rowsum": (C.c_int, [_P] * 10 + [DmShape, _P, _P, _P, *_ERR]),
     "dm_probe_mma": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
     "dm_device_status": (C.c_int, [C.POINTER(C.c_int32), *_ERR]),
+    "dm_kmean_partials": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_kmean_fold": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_fold_f32": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int64, C.c_int32, _P, _P, *_ERR]),
+    "dm_fwd_fp8_cp": (C.c_int, [_P] * 6 + [DmShape, DmCp, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
+    "dm_delta_fp8_cp": (C.c_int, [_P] * 9 + [DmShape, DmCp, C.c_int32, C.c_int32, _P, _P, *_ERR]),
+    "dm_bwd_workspace_bytes_cp": (C.c_int, [DmShape, DmCp, C.c_int32, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "dm_bwd_fp8_pass1_cp": (C.c_int, [_P] * 10 + [DmShape, DmCp, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, *_ERR]),
+    "dm_bwd_fp8_pass2_cp": (C.c_int, [_P] * 3 + [DmShape, DmCp, C.c_int32, C.c_int32, _P, _P, *_ERR]),
 }
 EXPORTS = tuple(_SIGNATURES)
 
@@ -186,68 +200,135 @@ def quant_do(dO_bnhd, o_bnhd=None):
     return codes, scales, delta
 
 
-def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=None):
-    """O (B, N, H, D) bf16 and LSE [B*H, N] fp32; with a head range only those heads are written."""
-    BH, N, D = Q8.shape
+def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=None, cp=None):
+    """O (B, N, H, D) bf16 and LSE [B*H, N] fp32; with a head range only those heads are written.  With a row map `cp`
+    (sequence split) Q8 holds the rank's nq local rows, K8 / V8 the whole sequence, and O / LSE are local."""
+    BH, nq, D = Q8.shape
+    N = K8.shape[1]
     hcount = H if hcount is None else hcount
     dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
         if out is None:
-            o = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
-            lse = torch.empty(B * H, N, device=dev, dtype=torch.float32)
+            o = torch.empty(B, nq, H, D, device=dev, dtype=torch.bfloat16)
+            lse = torch.empty(B * H, nq, device=dev, dtype=torch.float32)
         else:
             o, lse = out
-        _call("dm_fwd_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _shape(B, H, Hk, N, D, causal), h0,
-              hcount, _ptr(o), _ptr(lse), _stream(dev))
+        if cp is None:
+            _call("dm_fwd_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _shape(B, H, Hk, N, D, causal), h0,
+                  hcount, _ptr(o), _ptr(lse), _stream(dev))
+        else:
+            _call("dm_fwd_fp8_cp", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _shape(B, H, Hk, N, D, causal), cp,
+                  h0, hcount, _ptr(o), _ptr(lse), _stream(dev))
     return o, lse
 
 
-def delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, h0=0, hcount=None, out=None):
-    BH, N, D = Q8.shape
+def delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, h0=0, hcount=None, out=None, cp=None):
+    BH, nq, D = Q8.shape
+    N = K8.shape[1]
     hcount = H if hcount is None else hcount
     dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
-        delta = torch.empty(B * H, N, device=dev, dtype=torch.float32) if out is None else out
-        _call("dm_delta_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
-              _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(delta), _stream(dev))
+        delta = torch.empty(B * H, nq, device=dev, dtype=torch.float32) if out is None else out
+        if cp is None:
+            _call("dm_delta_fp8", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
+                  _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(delta), _stream(dev))
+        else:
+            _call("dm_delta_fp8_cp", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
+                  _shape(B, H, Hk, N, D, causal), cp, h0, hcount, _ptr(delta), _stream(dev))
     return delta
 
 
-def bwd_workspace_bytes(B, H, Hk, N, D, causal, hcount):
+def bwd_workspace_bytes(B, H, Hk, N, D, causal, hcount, cp=None):
     a, b = C.c_size_t(0), C.c_size_t(0)
-    rc = lib().dm_bwd_workspace_bytes(_shape(B, H, Hk, N, D, causal), hcount, C.byref(a), C.byref(b))
+    if cp is None:
+        rc = lib().dm_bwd_workspace_bytes(_shape(B, H, Hk, N, D, causal), hcount, C.byref(a), C.byref(b))
+    else:
+        rc = lib().dm_bwd_workspace_bytes_cp(_shape(B, H, Hk, N, D, causal), cp, hcount, C.byref(a), C.byref(b))
     if rc != 0:
         raise RuntimeError(f"delta_matching_b200.dm_bwd_workspace_bytes failed (code {rc})")
     return a.value, b.value
 
 
-def bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, h0=0, hcount=None, out=None, ws=None):
-    """dK, dV (B, N, H, D) bf16 per query head plus the dS' / psi workspace for pass 2."""
-    BH, N, D = Q8.shape
+def bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, h0=0, hcount=None, out=None, ws=None, cp=None,
+              out_fp32=False):
+    """dK, dV (B, N, H, D) per query head (bf16, or fp32 partials with out_fp32) plus the dS' / psi workspace for pass 2.
+    With a row map `cp` the Q-side inputs and the workspace hold the rank's local rows; dK / dV span the whole sequence."""
+    BH, nq, D = Q8.shape
+    N = K8.shape[1]
     hcount = H if hcount is None else hcount
     dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
         if out is None:
-            dk = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
-            dv = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
+            dt = torch.float32 if out_fp32 else torch.bfloat16
+            dk = torch.empty(B, N, H, D, device=dev, dtype=dt)
+            dv = torch.empty(B, N, H, D, device=dev, dtype=dt)
         else:
             dk, dv = out
         if ws is None:
-            nb_ds, nb_psi = bwd_workspace_bytes(B, H, Hk, N, D, causal, hcount)
+            nb_ds, nb_psi = bwd_workspace_bytes(B, H, Hk, N, D, causal, hcount, cp)
             ws = (torch.empty(nb_ds, device=dev, dtype=torch.uint8), torch.empty(nb_psi // 4, device=dev, dtype=torch.float32))
-        _call("dm_bwd_fp8_pass1", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
-              _ptr(delta), _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(dk), _ptr(dv), _ptr(ws[0]), _ptr(ws[1]), _stream(dev))
+        if cp is None and not out_fp32:
+            _call("dm_bwd_fp8_pass1", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s), _ptr(lse),
+                  _ptr(delta), _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(dk), _ptr(dv), _ptr(ws[0]), _ptr(ws[1]), _stream(dev))
+        else:
+            cpm = cp if cp is not None else DmCp(N, N // 128, 0, 0)
+            _call("dm_bwd_fp8_pass1_cp", _ptr(Q8), _ptr(K8), _ptr(V8), _ptr(dO8), _ptr(Q8s), _ptr(K8s), _ptr(V8s), _ptr(dO8s),
+                  _ptr(lse), _ptr(delta), _shape(B, H, Hk, N, D, causal), cpm, h0, hcount, 1 if out_fp32 else 0, _ptr(dk), _ptr(dv),
+                  _ptr(ws[0]), _ptr(ws[1]), _stream(dev))
     return dk, dv, ws
 
 
-def bwd_pass2(ws, K8, B, H, Hk, N, D, causal, h0=0, hcount=None, out=None):
+def bwd_pass2(ws, K8, B, H, Hk, N, D, causal, h0=0, hcount=None, out=None, cp=None):
     hcount = H if hcount is None else hcount
     dev = K8.device
+    nq = N if cp is None else cp.nq
     with torch.cuda.device(dev):
-        dq = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16) if out is None else out
-        _call("dm_bwd_fp8_pass2", _ptr(ws[0]), _ptr(ws[1]), _ptr(K8), _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(dq),
-              _stream(dev))
+        dq = torch.empty(B, nq, H, D, device=dev, dtype=torch.bfloat16) if out is None else out
+        if cp is None:
+            _call("dm_bwd_fp8_pass2", _ptr(ws[0]), _ptr(ws[1]), _ptr(K8), _shape(B, H, Hk, N, D, causal), h0, hcount, _ptr(dq),
+                  _stream(dev))
+        else:
+            _call("dm_bwd_fp8_pass2_cp", _ptr(ws[0]), _ptr(ws[1]), _ptr(K8), _shape(B, H, Hk, N, D, causal), cp, h0, hcount, _ptr(dq),
+                  _stream(dev))
     return dq
+
+
+def kmean_partials(k_bnhd):
+    """Per-64-row-chunk column sums [B*Hk, N_local/64, D] fp32 of a rank's local keys."""
+    B, N, Hk, D = k_bnhd.shape
+    k_bnhd = _unit_lane(k_bnhd)
+    with torch.cuda.device(k_bnhd.device):
+        part = torch.empty(B * Hk, N // 64, D, device=k_bnhd.device, dtype=torch.float32)
+        _call("dm_kmean_partials", _ptr(k_bnhd), _strides_bnhd(k_bnhd), B, Hk, N, D, _ptr(part), _stream(k_bnhd.device))
+    return part
+
+
+def kmean_fold(partials, B, Hk, N, D):
+    """The K mean [B*Hk, D] from all chunk sums of the sequence, [B*Hk, N/64, D] in sequence order."""
+    partials = partials.contiguous()
+    with torch.cuda.device(partials.device):
+        km = torch.empty(B * Hk, D, device=partials.device, dtype=torch.float32)
+        _call("dm_kmean_fold", _ptr(partials), B, Hk, N, D, _ptr(km), _stream(partials.device))
+    return km
+
+
+def fold_f32(x, count_dim, out_dtype=torch.float32):
+    """Sum a contiguous fp32 tensor over dimension `count_dim` in ascending order; the result (that dimension removed) is
+    rounded once to out_dtype (fp32 or bf16)."""
+    assert x.dtype == torch.float32 and out_dtype in (torch.float32, torch.bfloat16)
+    x = x.contiguous()
+    shape = list(x.shape)
+    outer = 1
+    for s_ in shape[:count_dim]:
+        outer *= s_
+    inner = 1
+    for s_ in shape[count_dim + 1:]:
+        inner *= s_
+    with torch.cuda.device(x.device):
+        out = torch.empty(shape[:count_dim] + shape[count_dim + 1:], device=x.device, dtype=out_dtype)
+        _call("dm_fold_f32", _ptr(x), outer, shape[count_dim], inner, 1 if out_dtype == torch.bfloat16 else 0, _ptr(out),
+              _stream(x.device))
+    return out
 
 
 def gqa_fold(x_bnhd, Hk):

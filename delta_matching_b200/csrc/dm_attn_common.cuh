@@ -21,6 +21,14 @@ __device__ __forceinline__ float phat(float s_raw, float dsc, float row_const) {
     return ex2(fminf(fmaf(s_raw, dsc, row_const), kMoE + 4.0f));
 }
 
+// Row map of the Q-side tensors (Q8, dO8, O, LSE, delta, dQ, dS' tiles): normally all N rows in order; under context
+// parallelism a rank holds two chunks of the sequence (zig-zag), `half` 128-row blocks starting at global block off0
+// followed by the rest starting at global block off1.  K-side tensors are always global.
+struct RowMap {
+    int nq, half, off0, off1;
+};
+__device__ __forceinline__ int global_block(const RowMap& m, int li) { return li < m.half ? m.off0 + li : m.off1 + (li - m.half); }
+
 // Problem coordinates of one CTA.
 struct HeadCoord {
     int b, h, bh, bhk;

@@ -76,6 +76,8 @@ struct Bwd1Params {
     float* psi;
     int H, Hk, N, h0, hcount, causal;
     int* status;
+    dm::RowMap rm;                                // which rows of the sequence the Q-side tensors hold
+    int out_fp32;                                 // dK / dV leave as fp32 (partials that another rank's are added to)
 };
 
 template <int kD>
@@ -91,9 +93,19 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
-    const int nbn = p.N / 128, nbm = p.N / 64;
+    const int nbn = p.N / 128;
+    const int nq_blk = p.rm.nq / 128, nbm = p.rm.nq / 64;   // local 128-row blocks and 64-row m-blocks
     const int J = blockIdx.x;                     // key block; J = 0 has the most m-blocks when causal and is launched first
-    const int m_lo = p.causal ? 2 * J : 0;
+    // m-blocks are counted in the local rows; global position grows with the local index, and both chunks of a row map
+    // start on a 128-row pair, so local and global m-block parity agree.  Causal: start at the first local m-block that is
+    // not wholly above the diagonal of key block J; a rank may hold none (n_it == 0: dK = dV = 0 for this block).
+    int m_lo = 0;
+    if (p.causal) {
+        const int rest = nq_blk - p.rm.half;
+        if (J < p.rm.off0 + p.rm.half) m_lo = 2 * max(J - p.rm.off0, 0);
+        else if (J < p.rm.off1 + rest) m_lo = 2 * (p.rm.half + max(J - p.rm.off1, 0));
+        else m_lo = nbm;
+    }
     const int n_it = nbm - m_lo;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
@@ -120,8 +132,8 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (warp >= 8) {
         // =============================================================== issuer warpgroup: TMA + tcgen05.mma, one lane
         dm::reg_dec<40>();
-        if (warp == 8 && lane == 0) {
-            const int q_row0 = hc.bh * p.N;
+        if (warp == 8 && lane == 0 && n_it > 0) {
+            const int q_row0 = hc.bh * p.rm.nq;
             const int kv_row0 = hc.bhk * p.N + J * 128;
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
@@ -171,7 +183,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dk, dsd + 4 * par + 2 * k, qd + 256 * k, idesc_dkv, k > 0);
                 dm::umma_commit(&s.bar_dkv_full);
                 if (par == 1 && zh == 0) {   // the pair's 128 x 128 dS' tile is complete: one TMA store to the workspace
-                    dm::tma_store_2d(&tm_ds, 0, (int)((((int64_t)bhl * nbn + ((m_lo + it) >> 1)) * nbn + J) * 128), s.ds[pp]);
+                    dm::tma_store_2d(&tm_ds, 0, (int)((((int64_t)bhl * nq_blk + ((m_lo + it) >> 1)) * nbn + J) * 128), s.ds[pp]);
                     dm::tma_store_commit();
                 }
             };
@@ -205,7 +217,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
         const int kgrp = key / kKPS;                  // K / V scale group inside the block
         const int khalf = key >> 6;                   // 64-key half (the psi tile at head_dim 256)
-        const int nsq = kD == 128 ? nbn : nbm;        // Q / dO scale blocks per head
+        const int nsq = kD == 128 ? nq_blk : nbm;     // Q / dO scale blocks per head
         auto sq_idx = [&](int mb_) { return kD == 128 ? (mb_ >> 1) : mb_; };
         const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
         const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
@@ -222,7 +234,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + rc_grp];
         auto fetch_rows = [&](int it, float& lse_v, float& dl_v) {
             if (tid < 64 * kGrp && it < n_it) {
-                const int64_t gi = (int64_t)hc.bh * p.N + (int64_t)(m_lo + it) * 64 + rc_r;
+                const int64_t gi = (int64_t)hc.bh * p.rm.nq + (int64_t)(m_lo + it) * 64 + rc_r;
                 lse_v = p.lse[gi];
                 dl_v = p.delta[gi];
             }
@@ -239,8 +251,8 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         fetch_rows(1, lse_n, dl_n);
         park_rows(1, lse_n, dl_n);
         fetch_rows(2, lse_n, dl_n);                    // parked during iteration 0
-        float q8sc_n = p.q8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)];
-        float do8sc_n = p.do8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)];
+        float q8sc_n = n_it > 0 ? p.q8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)] : 0.f;
+        float do8sc_n = n_it > 0 ? p.do8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)] : 0.f;
         float g_prev = 0.f, f_prev = 0.f;
         dm::named_bar_sync(1, kComputeThreads);
 
@@ -283,7 +295,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::tmem_ld_wait();
             dm::tc_fence_before();
             dm::mbar_arrive_warp(&s.bar_sp_free[sb]);      // this (S | dP) buffer may be overwritten
-            const bool diag = p.causal && (mb >> 1) == J;
+            const bool diag = p.causal && dm::global_block(p.rm, mb >> 1) == J;
             const int row_in_pair = par * 64 + g * 32;     // row offset of column 0 inside the 128-row pair
             float amax = 0.f;
             const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 32]);
@@ -355,12 +367,21 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             g_prev = g_cur;
             f_prev = dm::kMoInv * do8sc;
         }
-        fold(n_it - 1, g_prev, f_prev);
+        if (n_it > 0) fold(n_it - 1, g_prev, f_prev);
 
         // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
         const float ik = 1.0f / k8s_t;
         const int n_glob = J * 128 + key;
         const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128 + g * 64;
+        if (p.out_fp32) {
+            float4* ok = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dk) + off);
+            float4* ov = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dv) + off);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                ok[c] = make_float4(dk_acc[4 * c] * ik, dk_acc[4 * c + 1] * ik, dk_acc[4 * c + 2] * ik, dk_acc[4 * c + 3] * ik);
+                ov[c] = make_float4(dv_acc[4 * c], dv_acc[4 * c + 1], dv_acc[4 * c + 2], dv_acc[4 * c + 3]);
+            }
+        } else {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             uint32_t wk[4], wv[4];
@@ -374,6 +395,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             reinterpret_cast<uint4*>(p.dk + off)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
             reinterpret_cast<uint4*>(p.dv + off)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
         }
+        }
     }
     dm::tc_fence_before();
     __syncthreads();
@@ -381,6 +403,10 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 }
 
 }  // namespace
+
+namespace dmh {
+int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen);
+}
 
 extern "C" int dm_bwd_workspace_bytes(DmShape sh, int32_t hcount, size_t* ds8_bytes, size_t* psi_bytes) {
     if (!ds8_bytes || !psi_bytes || sh.N <= 0 || sh.N % 128 || sh.B <= 0 || hcount <= 0) return DM_ERR_ARG;
@@ -390,29 +416,49 @@ extern "C" int dm_bwd_workspace_bytes(DmShape sh, int32_t hcount, size_t* ds8_by
     return DM_OK;
 }
 
+extern "C" int dm_bwd_workspace_bytes_cp(DmShape sh, DmCp cp, int32_t hcount, size_t* ds8_bytes, size_t* psi_bytes) {
+    if (!ds8_bytes || !psi_bytes || sh.N <= 0 || sh.N % 128 || sh.B <= 0 || hcount <= 0 || sh.D != 128) return DM_ERR_ARG;
+    if (cp.nq <= 0 || cp.nq % 128 || cp.nq > sh.N) return DM_ERR_ARG;
+    *ds8_bytes = (size_t)sh.B * hcount * cp.nq * sh.N;
+    *psi_bytes = (size_t)sh.B * hcount * (cp.nq / 64) * (sh.N / 128) * sizeof(float);
+    return DM_OK;
+}
+
 extern "C" int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
                                 const float* v8s, const float* do8s, const float* lse, const float* delta, DmShape sh, int32_t h0,
                                 int32_t hcount, void* dk, void* dv, void* ds8_ws, float* psi_ws, void* stream, char* err, size_t errlen) {
+    DmCp cp{sh.N, sh.N / 128, 0, 0};
+    return dm_bwd_fp8_pass1_cp(q8, k8, v8, do8, q8s, k8s, v8s, do8s, lse, delta, sh, cp, h0, hcount, 0, dk, dv, ds8_ws, psi_ws, stream, err,
+                               errlen);
+}
+
+extern "C" int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                                   const float* v8s, const float* do8s, const float* lse, const float* delta, DmShape sh, DmCp cp,
+                                   int32_t h0, int32_t hcount, int32_t out_fp32, void* dk, void* dv, void* ds8_ws, float* psi_ws,
+                                   void* stream, char* err, size_t errlen) {
     int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
     if (rc) return rc;
+    const bool plain = cp.nq == sh.N && cp.half_blocks == sh.N / 128 && cp.off0 == 0;
+    if (!plain && (rc = dmh::check_cp(sh, cp, err, errlen))) return rc;
+    DM_REQUIRE(!out_fp32 || sh.D == 128, DM_ERR_UNSUPPORTED, "fp32 dK / dV partials are built for head_dim 128 only");
     const void* ptrs[] = {q8, k8, v8, do8, q8s, k8s, v8s, do8s, lse, delta, dk, dv, ds8_ws, psi_ws};
     const char* names[] = {"q8", "k8", "v8", "do8", "q8s", "k8s", "v8s", "do8s", "lse", "delta", "dk", "dv", "ds8_ws", "psi_ws"};
     for (int i = 0; i < 14; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     DM_REQUIRE(dmh::aligned16(dk) && dmh::aligned16(dv) && dmh::aligned16(ds8_ws), DM_ERR_ARG, "outputs and workspace must be 16-byte aligned");
-    const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
+    const uint64_t ntiles = (uint64_t)sh.B * hcount * (cp.nq / 128) * (sh.N / 128);
     DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads (got %llu tiles)",
                (unsigned long long)ntiles);
     CUtensorMap tq, td, tk, tv, ts;
-    if ((rc = dmh::make_tmap_u8(&tq, q8, sh.D, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&td, do8, sh.D, (uint64_t)sh.B * sh.H * sh.N, 64, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tq, q8, sh.D, (uint64_t)sh.B * sh.H * cp.nq, 64, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&td, do8, sh.D, (uint64_t)sh.B * sh.H * cp.nq, 64, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&ts, ds8_ws, 128, ntiles * 128, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
-                 sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
+                 sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status, dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, out_fp32};
     if (sh.D == 128) {
         const int smem = (int)sizeof(Bwd1Smem<128>) + 1024;
         static bool done[64] = {false};

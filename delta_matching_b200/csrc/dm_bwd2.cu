@@ -35,6 +35,7 @@ struct Bwd2Params {
     int H, Hk, N, h0, hcount, causal;
     float final_scale;
     int* status;
+    dm::RowMap rm;
 };
 
 __global__ void __launch_bounds__(256, 2)
@@ -47,8 +48,9 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
     const int nbn = p.N / 128, nbm = p.N / 64;
-    const int rb = nbn - 1 - (int)blockIdx.x;          // longest row blocks first
-    const int n_it = p.causal ? rb + 1 : nbn;
+    const int nq_blk = p.rm.nq / 128, nbm_l = p.rm.nq / 64;
+    const int rb = nq_blk - 1 - (int)blockIdx.x;       // local row block, longest first
+    const int n_it = p.causal ? dm::global_block(p.rm, rb) + 1 : nbn;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
     if (tid == 0) {
@@ -64,7 +66,7 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     dm::tc_fence_after();
     const uint32_t tmem = s.tmem_base;
     const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
-    const int64_t tile0 = ((int64_t)bhl * nbn + rb) * nbn;      // dS' tile index of (row block rb, key block 0)
+    const int64_t tile0 = ((int64_t)bhl * nq_blk + rb) * nbn;   // dS' tile index of (local row block rb, key block 0)
     const int kv_row0 = hc.bhk * p.N;
     constexpr uint32_t idesc = dm::idesc_e4m3(128, 128, true, true);
 
@@ -91,7 +93,7 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     }
 
     const int mb = 2 * rb + (row >> 6);
-    const float* psi_row = p.psi + ((int64_t)bhl * nbm + mb) * nbn;
+    const float* psi_row = p.psi + ((int64_t)bhl * nbm_l + mb) * nbn;
     float psi_max = 0.f;
     float dq[64];
 #pragma unroll
@@ -120,7 +122,7 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     }
 
     const int n_glob = rb * 128 + row;
-    __nv_bfloat16* op = p.dq + (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 128 + g * 64;
+    __nv_bfloat16* op = p.dq + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128 + g * 64;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         uint32_t w4[4];
@@ -255,16 +257,28 @@ bwd2_d256_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
 
 }  // namespace
 
+namespace dmh {
+int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen);
+}
+
 extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape sh, int32_t h0, int32_t hcount,
                                 void* dq, void* stream, char* err, size_t errlen) {
+    DmCp cp{sh.N, sh.N / 128, 0, 0};
+    return dm_bwd_fp8_pass2_cp(ds8_ws, psi_ws, k8, sh, cp, h0, hcount, dq, stream, err, errlen);
+}
+
+extern "C" int dm_bwd_fp8_pass2_cp(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape sh, DmCp cp, int32_t h0,
+                                   int32_t hcount, void* dq, void* stream, char* err, size_t errlen) {
     int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
     if (rc) return rc;
+    const bool plain = cp.nq == sh.N && cp.half_blocks == sh.N / 128 && cp.off0 == 0;
+    if (!plain && (rc = dmh::check_cp(sh, cp, err, errlen))) return rc;
     const void* ptrs[] = {ds8_ws, psi_ws, k8, dq};
     const char* names[] = {"ds8_ws", "psi_ws", "k8", "dq"};
     for (int i = 0; i < 4; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     DM_REQUIRE(dmh::aligned16(dq), DM_ERR_ARG, "dq must be 16-byte aligned");
-    const uint64_t ntiles = (uint64_t)sh.B * hcount * (sh.N / 128) * (sh.N / 128);
+    const uint64_t ntiles = (uint64_t)sh.B * hcount * (cp.nq / 128) * (sh.N / 128);
     DM_REQUIRE(ntiles * 128 < ((uint64_t)1 << 31), DM_ERR_ARG, "dS' workspace too large for one call: split the heads");
     CUtensorMap ts, tk;
     if ((rc = dmh::make_tmap_u8(&ts, ds8_ws, 128, ntiles * 128, 128, err, errlen))) return rc;
@@ -272,7 +286,8 @@ extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const v
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     const float sm = sh.D == 128 ? 0.08838834764831845f : 0.0625f;
-    Bwd2Params p{psi_ws, static_cast<__nv_bfloat16*>(dq), sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, sm / 256.0f, status};
+    Bwd2Params p{psi_ws, static_cast<__nv_bfloat16*>(dq), sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, sm / 256.0f, status,
+                 dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}};
     if (sh.D == 256) {
         const int smem = (int)sizeof(Bwd2Smem256) + 1024;
         DM_CUDA(cudaFuncSetAttribute(bwd2_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -290,7 +305,7 @@ extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const v
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    bwd2_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
+    bwd2_d128_kernel<<<dim3(cp.nq / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

@@ -49,6 +49,7 @@ struct DeltaParams {
     float* out_abs;          // debug mode only
     int H, Hk, N, h0, hcount, causal;
     int* status;
+    dm::RowMap rm;
 };
 
 template <bool kDebug, int kD>
@@ -63,7 +64,9 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const int row = (warp & 3) * 32 + lane;
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int nblk = p.N / 128;
-    const int I = nblk - 1 - (int)blockIdx.x;
+    const int nq_blk = p.rm.nq / 128;
+    const int li = nq_blk - 1 - (int)blockIdx.x;      // local row block
+    const int I = dm::global_block(p.rm, li);       // its place in the sequence
     const int n_tiles = p.causal ? I + 1 : nblk;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
@@ -82,7 +85,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     dm::tc_fence_after();
     const uint32_t tmem = s.tmem_base;
     const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
-    const int q_row0 = hc.bh * p.N + I * 128;
+    const int q_row0 = hc.bh * p.rm.nq + li * 128;
     const int kv_row0 = hc.bhk * p.N;
     constexpr uint32_t idesc = dm::idesc_e4m3(128, 128, false, false);
 
@@ -126,12 +129,12 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         issue(0);
     }
 
-    const int sq = kD == 128 ? (int)((int64_t)hc.bh * nblk + I) : (int)((int64_t)hc.bh * (p.N / 64) + 2 * I + (row >> 6));
+    const int sq = kD == 128 ? (int)((int64_t)hc.bh * nq_blk + li) : (int)((int64_t)hc.bh * (p.rm.nq / 64) + 2 * li + (row >> 6));
     const float q8sc = p.q8s[sq];
     const float do8sc = p.do8s[sq];
-    const int n_glob = I * 128 + row;
-    const float rc = dm::phat_row_const(p.lse[(int64_t)hc.bh * p.N + n_glob]);
-    const float dlt = kDebug ? p.delta_in[(int64_t)hc.bh * p.N + n_glob] : 0.f;
+    const int n_glob = li * 128 + row;              // row inside the (local) Q-side tensors
+    const float rc = dm::phat_row_const(p.lse[(int64_t)hc.bh * p.rm.nq + n_glob]);
+    const float dlt = kDebug ? p.delta_in[(int64_t)hc.bh * p.rm.nq + n_glob] : 0.f;
     double acc = 0.0, acc_abs = 0.0;
 
     for (int it = 0; it < n_tiles; ++it) {
@@ -183,8 +186,8 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     if (kDebug) s.part_abs[g][row] = acc_abs;
     __syncthreads();
     if (g == 0) {
-        p.out[(int64_t)hc.bh * p.N + n_glob] = (float)(s.part[0][row] + s.part[1][row]);
-        if (kDebug) p.out_abs[(int64_t)hc.bh * p.N + n_glob] = (float)(s.part_abs[0][row] + s.part_abs[1][row]);
+        p.out[(int64_t)hc.bh * p.rm.nq + n_glob] = (float)(s.part[0][row] + s.part[1][row]);
+        if (kDebug) p.out_abs[(int64_t)hc.bh * p.rm.nq + n_glob] = (float)(s.part_abs[0][row] + s.part_abs[1][row]);
     }
     if (warp == 0) dm::tmem_dealloc(tmem, 256);
 }
@@ -194,8 +197,8 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
            char* err, size_t errlen) {
     int rc;
     CUtensorMap tq, td, tk, tv;
-    if ((rc = dmh::make_tmap_u8(&tq, q8, kD, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
-    if ((rc = dmh::make_tmap_u8(&td, do8, kD, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tq, q8, kD, (uint64_t)sh.B * sh.H * p.rm.nq, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&td, do8, kD, (uint64_t)sh.B * sh.H * p.rm.nq, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     const int smem = (int)sizeof(DeltaSmem<kD>) + 1024;
@@ -208,18 +211,31 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    delta_kernel<kDebug, kD><<<dim3(sh.N / 128, sh.B * p.hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
+    delta_kernel<kDebug, kD><<<dim3(p.rm.nq / 128, sh.B * p.hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
 
 }  // namespace
 
+namespace dmh {
+int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen);
+}
+
 extern "C" int dm_delta_fp8(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
                             const float* v8s, const float* do8s, const float* lse, DmShape sh, int32_t h0, int32_t hcount, float* delta,
                             void* stream, char* err, size_t errlen) {
+    DmCp cp{sh.N, sh.N / 128, 0, 0};
+    return dm_delta_fp8_cp(q8, k8, v8, do8, q8s, k8s, v8s, do8s, lse, sh, cp, h0, hcount, delta, stream, err, errlen);
+}
+
+extern "C" int dm_delta_fp8_cp(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                               const float* v8s, const float* do8s, const float* lse, DmShape sh, DmCp cp, int32_t h0, int32_t hcount,
+                               float* delta, void* stream, char* err, size_t errlen) {
     int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
     if (rc) return rc;
+    const bool plain = cp.nq == sh.N && cp.half_blocks == sh.N / 128 && cp.off0 == 0;
+    if (!plain && (rc = dmh::check_cp(sh, cp, err, errlen))) return rc;
     const void* ptrs[] = {q8, k8, v8, do8, q8s, k8s, v8s, do8s, lse, delta};
     const char* names[] = {"q8", "k8", "v8", "do8", "q8s", "k8s", "v8s", "do8s", "lse", "delta"};
     for (int i = 0; i < 10; ++i)
@@ -227,7 +243,8 @@ extern "C" int dm_delta_fp8(const void* q8, const void* k8, const void* v8, cons
     DM_REQUIRE(sh.N % 128 == 0, DM_ERR_ARG, "seqlen must be a 128-multiple (got %d)", sh.N);
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
-    DeltaParams p{q8s, k8s, v8s, do8s, lse, nullptr, delta, nullptr, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
+    DeltaParams p{q8s, k8s, v8s, do8s, lse, nullptr, delta, nullptr, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status,
+                  dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}};
     return sh.D == 128 ? launch<false, 128>(q8, k8, v8, do8, p, sh, stream, err, errlen)
                        : launch<false, 256>(q8, k8, v8, do8, p, sh, stream, err, errlen);
 }
@@ -243,7 +260,8 @@ extern "C" int dm_bwd_dbg_rowsum(const void* q8, const void* k8, const void* v8,
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
-    DeltaParams p{q8s, k8s, v8s, do8s, lse, delta, rows, rows_abs, sh.H, sh.Hk, sh.N, 0, sh.H, sh.causal, status};
+    DeltaParams p{q8s, k8s, v8s, do8s, lse, delta, rows, rows_abs, sh.H, sh.Hk, sh.N, 0, sh.H, sh.causal, status,
+                  dm::RowMap{sh.N, sh.N / 128, 0, 0}};
     return sh.D == 128 ? launch<true, 128>(q8, k8, v8, do8, p, sh, stream, err, errlen)
                        : launch<true, 256>(q8, k8, v8, do8, p, sh, stream, err, errlen);
 }

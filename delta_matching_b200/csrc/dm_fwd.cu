@@ -42,6 +42,7 @@ struct FwdParams {
     float* lse;
     int H, Hk, N, h0, hcount, causal;
     int* status;
+    dm::RowMap rm;
 };
 
 __global__ void __launch_bounds__(256, 1)
@@ -54,7 +55,9 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int row = (warp & 3) * 32 + lane;   // query row inside the block = tensor-memory lane
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int nblk = p.N / 128;
-    const int I = nblk - 1 - (int)blockIdx.x;  // heaviest row blocks first
+    const int nq_blk = p.rm.nq / 128;
+    const int li = nq_blk - 1 - (int)blockIdx.x;  // local row block, heaviest first
+    const int I = dm::global_block(p.rm, li);   // its place in the sequence (decides the causal extent)
     const int n_tiles = p.causal ? I + 1 : nblk;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
@@ -79,7 +82,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t t_s = tmem, t_d0 = tmem + 128, t_d1 = tmem + 256;
     const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
 
-    const int q_row0 = hc.bh * p.N + I * 128;
+    const int q_row0 = hc.bh * p.rm.nq + li * 128;
     const int kv_row0 = hc.bhk * p.N;
     constexpr uint32_t idesc_s = dm::idesc_e4m3(128, 128, false, false);
     constexpr uint32_t idesc_pv = dm::idesc_e4m3(128, 128, false, true);
@@ -110,7 +113,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         issue_s(0);
     }
 
-    const float q8sc = p.q8s[(int64_t)hc.bh * nblk + I];
+    const float q8sc = p.q8s[(int64_t)hc.bh * nq_blk + li];
     float m_run = -INFINITY, l_part = 0.f;
     float o_acc[64];
 #pragma unroll
@@ -216,8 +219,8 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float l = s.lsum[0][row] + s.lsum[1][row];
     const bool dead = (l == 0.f) || (l != l);
     const float inv = dead ? 0.f : 1.0f / l;
-    const int n_glob = I * 128 + row;
-    __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * 128 + g * 64;
+    const int n_glob = li * 128 + row;          // row inside the (local) Q-side tensors
+    __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128 + g * 64;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         uint32_t w4[4];
@@ -228,7 +231,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
     }
-    if (g == 0) p.lse[(int64_t)hc.bh * p.N + n_glob] = dead ? -INFINITY : m_run + logf(l);
+    if (g == 0) p.lse[(int64_t)hc.bh * p.rm.nq + n_glob] = dead ? -INFINITY : m_run + logf(l);
     __syncthreads();
     if (warp == 0) dm::tmem_dealloc(tmem, 512);
 }
@@ -254,24 +257,55 @@ int launch_fwd_d256(const void* q8, const void* k8, const void* v8, const float*
                     int h0, int hcount, void* o, float* lse, void* stream, char* err, size_t errlen);
 }
 
+namespace dmh {
+int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen) {
+    DM_REQUIRE(s.D == 128, DM_ERR_UNSUPPORTED, "context-parallel row maps are built for head_dim 128 only");
+    DM_REQUIRE(cp.nq > 0 && cp.nq % 256 == 0 && cp.nq <= s.N, DM_ERR_ARG, "local seqlen must be a positive multiple of 256 (got %d)", cp.nq);
+    DM_REQUIRE(cp.half_blocks > 0 && cp.half_blocks % 2 == 0 && cp.half_blocks * 128 <= cp.nq, DM_ERR_ARG, "bad first-chunk size %d blocks", cp.half_blocks);
+    DM_REQUIRE(cp.off0 >= 0 && cp.off0 % 2 == 0 && (cp.off0 + cp.half_blocks) * 128 <= s.N, DM_ERR_ARG, "first chunk lies outside the sequence");
+    const int rest = cp.nq / 128 - cp.half_blocks;
+    DM_REQUIRE(rest == 0 || (cp.off1 % 2 == 0 && cp.off1 >= cp.off0 + cp.half_blocks && (cp.off1 + rest) * 128 <= s.N), DM_ERR_ARG,
+               "second chunk must follow the first and lie inside the sequence");
+    return DM_OK;
+}
+}  // namespace dmh
+
 extern "C" int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
                           DmShape sh, int32_t h0, int32_t hcount, void* o, float* lse, void* stream, char* err, size_t errlen) {
+    if (sh.D == 256) {
+        int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
+        if (rc) return rc;
+        const void* ptrs[] = {q8, k8, v8, q8s, k8s, v8s, o, lse};
+        const char* names[] = {"q8", "k8", "v8", "q8s", "k8s", "v8s", "o", "lse"};
+        for (int i = 0; i < 8; ++i)
+            if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
+        DM_REQUIRE(dmh::aligned16(q8) && dmh::aligned16(k8) && dmh::aligned16(v8) && dmh::aligned16(o), DM_ERR_ARG,
+                   "code and output pointers must be 16-byte aligned");
+        return dmh::launch_fwd_d256(q8, k8, v8, q8s, k8s, v8s, sh, h0, hcount, o, lse, stream, err, errlen);
+    }
+    DmCp cp{sh.N, sh.N / 128, 0, 0};
+    return dm_fwd_fp8_cp(q8, k8, v8, q8s, k8s, v8s, sh, cp, h0, hcount, o, lse, stream, err, errlen);
+}
+
+extern "C" int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
+                          DmShape sh, DmCp cp, int32_t h0, int32_t hcount, void* o, float* lse, void* stream, char* err, size_t errlen) {
     int rc = dmh::check_shape(sh, h0, hcount, err, errlen);
     if (rc) return rc;
+    if ((rc = dmh::check_cp(sh, cp, err, errlen))) return rc;
     const void* ptrs[] = {q8, k8, v8, q8s, k8s, v8s, o, lse};
     const char* names[] = {"q8", "k8", "v8", "q8s", "k8s", "v8s", "o", "lse"};
     for (int i = 0; i < 8; ++i)
         if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
     DM_REQUIRE(dmh::aligned16(q8) && dmh::aligned16(k8) && dmh::aligned16(v8) && dmh::aligned16(o), DM_ERR_ARG,
                "code and output pointers must be 16-byte aligned");
-    if (sh.D == 256) return dmh::launch_fwd_d256(q8, k8, v8, q8s, k8s, v8s, sh, h0, hcount, o, lse, stream, err, errlen);
     CUtensorMap tq, tk, tv;
-    if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::make_tmap_u8(&tq, q8, 128, (uint64_t)sh.B * sh.H * cp.nq, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, 128, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
-    FwdParams p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
+    FwdParams p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status,
+                dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}};
     const int smem = (int)sizeof(FwdSmem) + 1024;
     {
         static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
@@ -282,7 +316,7 @@ extern "C" int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const 
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    fwd_d128_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+    fwd_d128_kernel<<<dim3(cp.nq / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

@@ -234,6 +234,85 @@ extern "C" int dm_kmean(const void* k, DmStrides ks, int32_t B, int32_t Hk, int3
     return DM_OK;
 }
 
+// The two halves of dm_kmean on their own, for a sequence that is split across ranks: every rank sums its own 64-row
+// chunks, the partial sums are exchanged and laid out in sequence order, and every rank folds all of them in that order,
+// which gives the bits dm_kmean gives on the whole sequence.
+extern "C" int dm_kmean_partials(const void* k, DmStrides ks, int32_t B, int32_t Hk, int32_t N, int32_t D, float* partials, void* stream,
+                                 char* err, size_t errlen) {
+    int rc = check_geometry(B, Hk, N, D, err, errlen);
+    if (rc) return rc;
+    if ((rc = dmh::check_device_ptr(k, "k", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(partials, "partials", err, errlen))) return rc;
+    if ((rc = check_strides(k, ks, D, "k", err, errlen))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(k);
+    if (D == 128) kmean_partial_kernel<128><<<dim3(N / 64 / 4, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
+    else kmean_partial_kernel<256><<<dim3(N / 64 / 2, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+extern "C" int dm_kmean_fold(const float* partials, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, void* stream, char* err,
+                             size_t errlen) {
+    int rc = check_geometry(B, Hk, N, D, err, errlen);
+    if (rc) return rc;
+    if ((rc = dmh::check_device_ptr(partials, "partials", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(km, "km", err, errlen))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (D == 128) kmean_fold_kernel<128><<<B * Hk, 128, 0, st>>>(partials, N, km);
+    else kmean_fold_kernel<256><<<B * Hk, 256, 0, st>>>(partials, N, km);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+// ---- ordered fp32 fold ----------------------------------------------------------------------------------------------
+// out[o, i] = sum over c ascending of in[o, c, i]: the fold of fp32 dK / dV partials over the query heads of a KV group
+// (count = H / Hk, inner = D) and over the ranks of a sequence split (outer = 1, count = ranks), in a fixed order so the
+// result does not depend on timing.  Four floats per thread; the result is rounded once, to bf16 when asked.
+namespace {
+__global__ void __launch_bounds__(256) fold_f32_kernel(const float4* __restrict__ in, int64_t outer, int count, int64_t inner4,
+                                                       float4* __restrict__ out_f32, uint2* __restrict__ out_bf16) {
+    const int64_t total = outer * inner4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t o = i / inner4, r = i - o * inner4;
+        const float4* p = in + o * count * inner4 + r;
+        float4 a = p[0];
+        for (int c = 1; c < count; ++c) {
+            const float4 b = p[(int64_t)c * inner4];
+            a.x = __fadd_rn(a.x, b.x);
+            a.y = __fadd_rn(a.y, b.y);
+            a.z = __fadd_rn(a.z, b.z);
+            a.w = __fadd_rn(a.w, b.w);
+        }
+        if (out_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+            out_bf16[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else {
+            out_f32[i] = a;
+        }
+    }
+}
+}  // namespace
+
+extern "C" int dm_fold_f32(const float* in, int64_t outer, int32_t count, int64_t inner, int32_t out_is_bf16, void* out, void* stream,
+                           char* err, size_t errlen) {
+    DM_REQUIRE(outer > 0 && count > 0 && inner > 0 && inner % 4 == 0, DM_ERR_ARG,
+               "dm_fold_f32: outer, count, inner must be positive and inner a multiple of 4 (got %lld, %d, %lld)", (long long)outer, count,
+               (long long)inner);
+    int rc;
+    if ((rc = dmh::check_device_ptr(in, "in", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(out, "out", err, errlen))) return rc;
+    DM_REQUIRE(dmh::aligned16(in) && dmh::aligned16(out), DM_ERR_ARG, "dm_fold_f32: pointers must be 16-byte aligned");
+    const int64_t total = outer * (inner / 4);
+    const int64_t want = (total + 255) / 256;
+    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    fold_f32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(in), outer, count, inner / 4, out_is_bf16 ? nullptr : static_cast<float4*>(out),
+        out_is_bf16 ? static_cast<uint2*>(out) : nullptr);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
 template <int D, int MODE>
 static void launch_quant(const void* x, DmStrides xs, const void* o, DmStrides os, const float* km, void* codes, float* scales,
                          float* delta, int B, int heads, int N, cudaStream_t st) {

@@ -42,6 +42,16 @@ typedef struct DmStrides {
     int64_t b, n, h;
 } DmStrides;
 
+/* Context parallelism (sequence split across ranks, used for the long-context config): a rank's Q-side tensors (Q8, dO8
+ * and their scales, O, LSE, delta, dQ, the dS' workspace) hold only `nq` local rows = two chunks of the sequence (zig-zag
+ * balance for causal attention): `half_blocks` 128-row blocks that start at global 128-row block `off0`, then the rest
+ * starting at global block `off1` (off0 < off1, both even).  K-side tensors (K8, V8, their scales, dK, dV) always span the
+ * whole sequence N.  The *_cp entry points take this map; the plain ones are the map {N, N / 128, 0, 0}.  head_dim 128 only.
+ * No counterpart in the reference, which has no sequence parallelism (its long-context tool is the head split). */
+typedef struct DmCp {
+    int32_t nq, half_blocks, off0, off1;
+} DmCp;
+
 /* Library identity: version, numerics tag, build flags.  Replaces torch.ops.delta_matching.build_hd128 / build_gt /
  * build_bf16dp (csrc/delta_matching_api.cpp:684-704) and feeds kernel_version() (delta_matching/__init__.py:65-89). */
 const char* dm_build_info(void);
@@ -87,11 +97,31 @@ int dm_quant_do(const void* do_bf16, DmStrides dos, const void* o_bf16, DmStride
 int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
                DmShape s, int32_t h0, int32_t hcount, void* o_bf16, float* lse, void* stream, char* err, size_t errlen);
 
+/* The two halves of dm_kmean for a sequence split across ranks: each rank's per-64-row-chunk sums [B*Hk, N_local/64, D],
+ * then (after the exchange, partials in sequence order [B*Hk, N/64, D]) the fold and the division by N.  Same bits as
+ * dm_kmean on the whole sequence.  No counterpart in the reference. */
+int dm_kmean_partials(const void* k, DmStrides ks, int32_t B, int32_t Hk, int32_t N_local, int32_t D, float* partials, void* stream,
+                      char* err, size_t errlen);
+int dm_kmean_fold(const float* partials, int32_t B, int32_t Hk, int32_t N, int32_t D, float* km, void* stream, char* err, size_t errlen);
+
+/* out[o, i] = sum over c (ascending) of in[o, c, i], fp32 in, fp32 or bf16 out: folds fp32 dK / dV partials over the query
+ * heads of a KV group and over the ranks of a sequence split in a fixed order.  inner % 4 == 0.  No counterpart in the
+ * reference (its GQA fold is dm_gqa_fold's). */
+int dm_fold_f32(const float* in, int64_t outer, int32_t count, int64_t inner, int32_t out_is_bf16, void* out, void* stream, char* err,
+                size_t errlen);
+
+int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
+                  DmShape s, DmCp cp, int32_t h0, int32_t hcount, void* o_bf16, float* lse, void* stream, char* err, size_t errlen);
+
 /* Pass 0: the matched delta [B*H, N] fp32 from the backward's own fp8 P-hat / dP pair.
  * Replaces torch.ops.delta_matching.delta_fp8 (csrc/delta_matching_api.cpp:471-600). */
 int dm_delta_fp8(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
                  const float* v8s, const float* do8s, const float* lse, DmShape s, int32_t h0, int32_t hcount, float* delta,
                  void* stream, char* err, size_t errlen);
+
+int dm_delta_fp8_cp(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                    const float* v8s, const float* do8s, const float* lse, DmShape s, DmCp cp, int32_t h0, int32_t hcount,
+                    float* delta, void* stream, char* err, size_t errlen);
 
 /* Workspace of the backward for `hcount` query heads per batch: dS' code tiles (e4m3) and their psi scales (fp32).
  * Replaces the allocations in bwd_fp8_core (csrc/delta_matching_api.cpp:288-306). */
@@ -106,6 +136,17 @@ int dm_bwd_fp8_pass1(const void* q8, const void* k8, const void* v8, const void*
                      size_t errlen);
 int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape s, int32_t h0, int32_t hcount,
                      void* dq_bf16, void* stream, char* err, size_t errlen);
+
+/* Context-parallel forms.  The workspace holds the local rows only: dS' [B*hcount, nq/128, N/128, 128, 128], psi
+ * [B*hcount, nq/64, N/128].  Pass 1 produces this rank's PARTIAL dK / dV over its local rows for every key of the sequence,
+ * (B, N, H, D) per query head, as fp32 when out_fp32 != 0 (so the cross-rank sum is rounded once) else bf16. */
+int dm_bwd_workspace_bytes_cp(DmShape s, DmCp cp, int32_t hcount, size_t* ds8_bytes, size_t* psi_bytes);
+int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
+                        const float* v8s, const float* do8s, const float* lse, const float* delta, DmShape s, DmCp cp, int32_t h0,
+                        int32_t hcount, int32_t out_fp32, void* dk, void* dv, void* ds8_ws, float* psi_ws, void* stream, char* err,
+                        size_t errlen);
+int dm_bwd_fp8_pass2_cp(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape s, DmCp cp, int32_t h0, int32_t hcount,
+                        void* dq_bf16, void* stream, char* err, size_t errlen);
 
 /* GQA fold: per-query-head grads (B, N, H, D) bf16 -> (B, N, Hk, D) bf16, fp32 sum over the H/Hk heads of a KV head in
  * ascending head order, one bf16 rounding.  Replaces dk.reshape(B, Hk, rep, N, D).sum(2) (delta_matching/attn.py:111-118). */
