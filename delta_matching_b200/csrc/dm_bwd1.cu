@@ -132,18 +132,25 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (warp >= 8) {
         // =============================================================== issuer warpgroup: TMA + tcgen05.mma, one lane
         dm::reg_dec<40>();
+        const int kv_row0 = hc.bhk * p.N + J * 128;
         if (warp == 8 && lane == 0 && n_it > 0) {
-            const int q_row0 = hc.bh * p.rm.nq;
-            const int kv_row0 = hc.bhk * p.N + J * 128;
+            // Everything this thread touches per m-block is a handful of 32-bit words: descriptor low words (address >> 4)
+            // of the operand buffers and the row coordinate of the next Q / dO tile.
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
-            const uint64_t ptd = dm::smem_desc_sw128(dm::smem_u32(s.pt));
+            constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;   // descriptor strides
+            const uint32_t k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
+            const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
+            const uint32_t pt_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.pt)), ds_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.ds[0]));
+            const int q_row0 = hc.bh * p.rm.nq + m_lo * 64;
+            const int ds_row0 = (int)((((int64_t)bhl * nq_blk + (m_lo >> 1)) * nbn + J) * 128);   // dS' tile of the first row pair
             auto load_qdo = [&](int it) {
-                const int st = it % kStages, mb = m_lo + it;
+                const int st = it % kStages;
                 dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
+#pragma unroll
                 for (int hh = 0; hh < kDH; ++hh) {
-                    dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + mb * 64, &s.bar_qdo[st]);
-                    dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + mb * 64, &s.bar_qdo[st]);
+                    dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
+                    dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
                 }
             };
             // descriptor low words advance by bytes >> 4: 32 bytes of K = 2, 4096 bytes (32 rows) = 256, 64 bytes = 4
@@ -153,37 +160,40 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
                 dm::tc_fence_after();
                 const uint32_t t_s = tmem + b * 128, t_dp = t_s + 64;
+                const uint32_t qs = q_lo + st * kStageQ, dos = do_lo + st * kStageQ;
 #pragma unroll
                 for (int hh = 0; hh < kDH; ++hh) {
-                    const uint64_t kd = dm::smem_desc_sw128(dm::smem_u32(s.k[hh])), qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st][hh]));
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_s, kd + 2 * k, qd + 2 * k, idesc_sp, (hh | k) != 0);
+                    for (int k = 0; k < 4; ++k) {
+                        if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_s, k_lo, qs, idesc_sp);
+                        else dm::umma_e4m3_lo<true>(t_s, k_lo + hh * kSub + 2 * k, qs + hh * kSubQ + 2 * k, idesc_sp);
+                    }
                 }
 #pragma unroll
                 for (int hh = 0; hh < kDH; ++hh) {
-                    const uint64_t vd = dm::smem_desc_sw128(dm::smem_u32(s.v[hh])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st][hh]));
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) dm::umma_e4m3(t_dp, vd + 2 * k, dd + 2 * k, idesc_sp, (hh | k) != 0);
+                    for (int k = 0; k < 4; ++k) {
+                        if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_dp, v_lo, dos, idesc_sp);
+                        else dm::umma_e4m3_lo<true>(t_dp, v_lo + hh * kSub + 2 * k, dos + hh * kSubQ + 2 * k, idesc_sp);
+                    }
                 }
                 dm::umma_commit(&s.bar_sp_full[b]);
             };
             auto issue_dkv = [&](int it) {
-                const int st = it % kStages, par = (m_lo + it) & 1;
+                const int st = it % kStages, par = (m_lo + it) & 1, pp = ((m_lo + it) >> 1) & 1;
                 dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
                 if (it >= 1) dm::mbar_wait(&s.bar_dkv_free, (it - 1) & 1, wc);
                 dm::tc_fence_after();
-                const uint64_t qd = dm::smem_desc_sw128(dm::smem_u32(s.q[st][zh])), dd = dm::smem_desc_sw128(dm::smem_u32(s.dO[st][zh]));
+                const uint32_t qs = q_lo + st * kStageQ + zh * kSubQ, dos = do_lo + st * kStageQ + zh * kSubQ;
+                const uint32_t pa = pt_lo + 4 * par, da = ds_lo + pp * kSub + 4 * par;
                 // head_dim 128: dV_tmp accumulates the two m-blocks of a 128-row dO scale block; head_dim 256: one m-block
-#pragma unroll
-                for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dv, ptd + 4 * par + 2 * k, dd + 256 * k, idesc_dkv, (kD == 128 && par != 0) || k > 0);
-#pragma unroll
-                const int pp = ((m_lo + it) >> 1) & 1;                       // parity of the 128-row pair
-                const uint64_t dsd = dm::smem_desc_sw128(dm::smem_u32(s.ds[pp]));
-#pragma unroll
-                for (int k = 0; k < 2; ++k) dm::umma_e4m3(t_dk, dsd + 4 * par + 2 * k, qd + 256 * k, idesc_dkv, k > 0);
+                dm::umma_e4m3_lo_rt(t_dv, pa, dos, idesc_dkv, (kD == 128 && par != 0) ? 1u : 0u);
+                dm::umma_e4m3_lo<true>(t_dv, pa + 2, dos + 256, idesc_dkv);
+                dm::umma_e4m3_lo<false>(t_dk, da, qs, idesc_dkv);
+                dm::umma_e4m3_lo<true>(t_dk, da + 2, qs + 256, idesc_dkv);
                 dm::umma_commit(&s.bar_dkv_full);
                 if (par == 1 && zh == 0) {   // the pair's 128 x 128 dS' tile is complete: one TMA store to the workspace
-                    dm::tma_store_2d(&tm_ds, 0, (int)((((int64_t)bhl * nq_blk + ((m_lo + it) >> 1)) * nbn + J) * 128), s.ds[pp]);
+                    dm::tma_store_2d(&tm_ds, 0, ds_row0 + ((it + (m_lo & 1)) >> 1) * (nbn * 128), s.ds[pp]);
                     dm::tma_store_commit();
                 }
             };
@@ -222,6 +232,8 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
         const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
+        // the local 128-row block on the diagonal of this key block (none: -1); it is the first one of the causal loop
+        const int diag_lb = (p.causal && n_it > 0 && dm::global_block(p.rm, m_lo >> 1) == J) ? (m_lo >> 1) : -1;
         float g_max = 0.f;
         float dk_acc[64], dv_acc[64];
 #pragma unroll
@@ -288,34 +300,44 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::mbar_wait(&s.bar_sp_full[sb], (it >> 1) & 1, wc);
             dm::tc_fence_after();
 
-            // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory
+            // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory.  S^T first: the exponentials run while
+            // dP^T is still on its way from tensor memory.
             float sv[32], ds[32];
             dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
-            dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128 + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
             dm::tmem_ld_wait();
-            dm::tc_fence_before();
-            dm::mbar_arrive_warp(&s.bar_sp_free[sb]);      // this (S | dP) buffer may be overwritten
-            const bool diag = p.causal && dm::global_block(p.rm, mb >> 1) == J;
+            dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128 + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
+            const bool diag = (mb >> 1) == diag_lb;
             const int row_in_pair = par * 64 + g * 32;     // row offset of column 0 inside the 128-row pair
-            float amax = 0.f;
             const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 32]);
             const float4* dl4 = reinterpret_cast<const float4*>(&s.dlk[rb][kgrp][g * 32]);
-            float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
-                const float4 r4 = rc4[c4], d4 = dl4[c4];
-                const float rcv[4] = {r4.x, r4.y, r4.z, r4.w}, dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+                const float4 r4 = rc4[c4];
+                const float rcv[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int c = 4 * c4 + e;
                     float ph = dm::phat(sv[c], dsc, rcv[e]);
                     if (diag && key > row_in_pair + c) ph = 0.f;
                     sv[c] = ph;
-                    ds[c] = ph * (ds[c] * dpk - dlv[e]);
+                }
+            }
+            dm::tmem_ld_wait();
+            dm::tc_fence_before();
+            dm::mbar_arrive_warp(&s.bar_sp_free[sb]);      // this (S | dP) buffer may be overwritten
+            float am4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c4 = 0; c4 < 8; ++c4) {
+                const float4 d4 = dl4[c4];
+                const float dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = 4 * c4 + e;
+                    ds[c] = sv[c] * (ds[c] * dpk - dlv[e]);
                     am4[e] = fmaxf(am4[e], fabsf(ds[c]));
                 }
             }
-            amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
+            float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
             {
                 uint32_t w[8];
 #pragma unroll
@@ -323,9 +345,25 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
             }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            // the warp's maximum in one instruction: non-negative floats order like their bit patterns
+            amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
             if (lane == 0) s.amax[sb][warp] = amax;
+            // The previous m-block's dK product starts its way into the registers that held P-hat, under the barrier and
+            // the psi arithmetic.
+            uint32_t stage[16];
+            const bool dv_fold = kD == 256 || ((mb - 1) & 1) == 1;     // m-block it - 1 closed a dO scale block
+            // one 16-column chunk of a product buffer into the accumulators, and the next chunk set off
+#define DM_FOLD_CHUNK(ACC, SCALE, OFF)                                                                           \
+            {                                                                                                    \
+                dm::tmem_ld_wait();                                                                              \
+                _Pragma("unroll") for (int i = 0; i < 16; ++i)                                                   \
+                    ACC[(OFF) + i] = fmaf(__uint_as_float(stage[i]), SCALE, ACC[(OFF) + i]);                     \
+            }
+            if (it > 0) {
+                dm::mbar_wait(&s.bar_dkv_full, (it - 1) & 1, wc);
+                dm::tc_fence_after();
+                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64), stage);
+            }
             dm::named_bar_sync(1, kComputeThreads);
             if (kD == 128) {
 #pragma unroll
@@ -338,7 +376,11 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             fetch_rows(it + 3, lse_n, dl_n);
             const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
             const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
-            const float psi = fmaxf(psi_raw, g_max * (256.0f * 1e-8f) / q8sc);
+            // psi = max(psi_raw, g_max * 256e-8 / q8sc); the quotient can only win when its numerator exceeds
+            // psi_raw * q8sc, so the division is formed only then (the 1 % margin covers the rounding of both sides)
+            float psi = psi_raw;
+            const float fl_num = g_max * (256.0f * 1e-8f);
+            if (fl_num > psi_raw * q8sc * 0.99f) psi = fmaxf(psi_raw, fl_num / q8sc);
             const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
             const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
             g_max = fmaxf(g_max, g_cur);
@@ -349,21 +391,50 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                     p.psi[((int64_t)bhl * nbm + mb) * nbm + 2 * J + khalf] = tile_zero ? 0.f : psi;
                 }
             }
+            if (it > 0) {
+                DM_FOLD_CHUNK(dk_acc, g_prev, 0)
+                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64 + 16), stage);
+            }
 
-            // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
+            // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2; the previous m-block's
+            // dK product keeps arriving in 16-column chunks between the halves
+            uint8_t* dst = s.ds[(mb >> 1) & 1];
             {
-                uint32_t w[8];
+                uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
+                for (int c = 0; c < 4; ++c)
                     w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
-                uint8_t* dst = s.ds[(mb >> 1) & 1];
                 *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+            if (it > 0) {
+                DM_FOLD_CHUNK(dk_acc, g_prev, 16)
+                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), stage);
+            }
+            {
+                uint32_t w[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    w[c] = dm::cvt_e4m3x4(ds[16 + 4 * c] * psi_inv, ds[17 + 4 * c] * psi_inv, ds[18 + 4 * c] * psi_inv, ds[19 + 4 * c] * psi_inv);
+                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[sb]);
-            // ---- the previous m-block's products, complete by now, go into the accumulators
-            if (it > 0) fold(it - 1, g_prev, f_prev);
+            // ---- the rest of the previous m-block's products
+            if (it > 0) {
+                DM_FOLD_CHUNK(dk_acc, g_prev, 32)
+                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64 + 48), stage);
+                DM_FOLD_CHUNK(dk_acc, g_prev, 48)
+                if (dv_fold) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        dm::tmem_ld16(dm::tmem_addr(t_dv, lane_base, g * 64 + 16 * q4), stage);
+                        DM_FOLD_CHUNK(dv_acc, f_prev, 16 * q4)
+                    }
+                }
+                dm::tc_fence_before();
+                dm::mbar_arrive_warp(&s.bar_dkv_free);
+            }
+#undef DM_FOLD_CHUNK
             g_prev = g_cur;
             f_prev = dm::kMoInv * do8sc;
         }

@@ -178,6 +178,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                          // layout type: 128-byte swizzle
     return d;
 }
+// The same descriptor as two 32-bit words: only the low word depends on the address, so an issuing thread keeps one
+// register per buffer and advances it by (bytes >> 4); the high word is a constant.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo_sw128(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+
 // Instruction descriptor, kind::f8f6f4, e4m3 x e4m3 -> fp32, dense.
 __host__ __device__ constexpr uint32_t idesc_e4m3(int M, int N, bool a_mn_major, bool b_mn_major) {
     return (1u << 4)                               // D format fp32
@@ -192,6 +197,28 @@ __device__ __forceinline__ void umma_e4m3(uint32_t d_tmem, uint64_t adesc, uint6
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same with descriptors given by their low words (high word = kDescHiSw128) and a compile-time accumulate flag.
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_e4m3_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "n"(kAccumulate ? 1 : 0), "n"(kDescHiSw128)
+        : "memory");
+}
+__device__ __forceinline__ void umma_e4m3_lo_rt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(kDescHiSw128)
         : "memory");
 }
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed (implies fence::before_thread_sync).
