@@ -2,9 +2,10 @@
 // pass 2 (csrc/mainloop_bwd_sm90_fp8r.hpp:695-952 of the reference, restated for tcgen05).
 //
 // One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  384 threads:
-// warps 0..7 compute (232 registers each after setmaxnreg), warp 8 of the third warpgroup issues every TMA copy and every
-// tcgen05.mma (one lane) so that descriptor building and instruction issue never sit on the compute warps' path.  The two
-// sides meet only through mbarriers.
+// warps 0..7 compute (232 registers each after setmaxnreg); warps 8..11, one per scheduler, each run one service loop so
+// that no instruction issue sits on the compute warps' path and no service waits behind another: warp 8 issues the S^T /
+// dP^T tcgen05.mma, warp 9 the dK / dV tcgen05.mma and the dS' TMA store, warp 10 the TMA loads, warp 11 produces the
+// per-row constants.  The sides meet only through mbarriers.
 // Everything is computed transposed (keys x rows): tensor-memory lane = key, so the per-key scales are per-thread
 // constants.  Per m-block:
 //   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each into one of two (S | dP) tensor-memory buffers, issued
@@ -57,8 +58,10 @@ struct Bwd1Smem {
     alignas(1024) uint8_t ds[2][kTile];   // dS' codes, same layout, one tile per 128-row pair parity (a TMA store drains the other)
     alignas(16) float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
     alignas(16) float dlk[3][kGrp][64];               // delta * k8s(group) per row
+    float sc[3][2];                                   // q8sc, do8sc of the m-block (same ring)
     float amax[2][8];
-    uint64_t bar_kv, bar_qdo[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full, bar_dkv_free;
+    uint64_t bar_kv, bar_qdo[kStages], bar_stage_free[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full,
+        bar_dkv_free, bar_ds_free[2], bar_rows_full[3], bar_rows_free[3];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -112,11 +115,19 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (tid == 0) {
         s.abort_flag = 0;
         dm::mbar_init(&s.bar_kv, 1);
-        for (int i = 0; i < kStages; ++i) dm::mbar_init(&s.bar_qdo[i], 1);
+        for (int i = 0; i < kStages; ++i) {
+            dm::mbar_init(&s.bar_qdo[i], 1);
+            dm::mbar_init(&s.bar_stage_free[i], 1);
+        }
+        for (int i = 0; i < 3; ++i) {
+            dm::mbar_init(&s.bar_rows_full[i], 1);
+            dm::mbar_init(&s.bar_rows_free[i], 1);
+        }
         for (int i = 0; i < 2; ++i) {
             dm::mbar_init(&s.bar_sp_full[i], 1);
             dm::mbar_init(&s.bar_sp_free[i], 8);
             dm::mbar_init(&s.bar_codes[i], 8);
+            dm::mbar_init(&s.bar_ds_free[i], 1);
         }
         dm::mbar_init(&s.bar_dkv_full, 1);
         dm::mbar_init(&s.bar_dkv_free, 8);
@@ -130,95 +141,139 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const uint32_t t_dv = tmem + 256, t_dk = tmem + 384;
 
     if (warp >= 8) {
-        // =============================================================== issuer warpgroup: TMA + tcgen05.mma, one lane
+        // =============================================================== service warps 8..11, one per scheduler
+        // Each runs its loop converged (all lanes wait and compute the same addresses, so they stay in uniform registers)
+        // and lane 0 alone executes the asynchronous instruction.
         dm::reg_dec<40>();
+        const bool leader = lane == 0;
         const int kv_row0 = hc.bhk * p.N + J * 128;
-        if (warp == 8 && lane == 0 && n_it > 0) {
-            // Everything this thread touches per m-block is a handful of 32-bit words: descriptor low words (address >> 4)
-            // of the operand buffers and the row coordinate of the next Q / dO tile.
+        if (warp == 8) {
+            // ---- S^T = K Q^T and dP^T = V dO^T of m-block `it` into product buffer it & 1, up to two m-blocks ahead
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
-            constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
             constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;   // descriptor strides
             const uint32_t k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
             const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
-            const uint32_t pt_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.pt)), ds_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.ds[0]));
-            const int q_row0 = hc.bh * p.rm.nq + m_lo * 64;
-            const int ds_row0 = (int)((((int64_t)bhl * nq_blk + (m_lo >> 1)) * nbn + J) * 128);   // dS' tile of the first row pair
-            auto load_qdo = [&](int it) {
-                const int st = it % kStages;
-                dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
-#pragma unroll
-                for (int hh = 0; hh < kDH; ++hh) {
-                    dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
-                    dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
-                }
-            };
-            // descriptor low words advance by bytes >> 4: 32 bytes of K = 2, 4096 bytes (32 rows) = 256, 64 bytes = 4
-            auto issue_sp = [&](int it) {
+            if (n_it > 0) dm::mbar_wait(&s.bar_kv, 0, wc);
+            for (int it = 0; it < n_it; ++it) {
                 const int st = it % kStages, b = it & 1;
                 if (it >= 2) dm::mbar_wait(&s.bar_sp_free[b], ((it - 2) >> 1) & 1, wc);
                 dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
+                // the compute warps read the row constants of this m-block once its products are there: waiting here saves
+                // them a wait of their own
+                dm::mbar_wait(&s.bar_rows_full[it % 3], (it / 3) & 1, wc);
+                // The compute warps write the dS' codes of this m-block into the tile of its row pair; the TMA store that
+                // drains the pair two back must have read that tile.  Gating the products gates the compute warps.
+                const int pair = it >> 1;           // m_lo is even: pairs start at it = 0
+                if (zh == 0 && (it & 1) == 0 && pair >= 2) dm::mbar_wait(&s.bar_ds_free[pair & 1], ((pair - 2) >> 1) & 1, wc);
                 dm::tc_fence_after();
                 const uint32_t t_s = tmem + b * 128, t_dp = t_s + 64;
                 const uint32_t qs = q_lo + st * kStageQ, dos = do_lo + st * kStageQ;
+                if (leader) {
 #pragma unroll
-                for (int hh = 0; hh < kDH; ++hh) {
+                    for (int hh = 0; hh < kDH; ++hh) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_s, k_lo, qs, idesc_sp);
-                        else dm::umma_e4m3_lo<true>(t_s, k_lo + hh * kSub + 2 * k, qs + hh * kSubQ + 2 * k, idesc_sp);
+                        for (int k = 0; k < 4; ++k) {
+                            if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_s, k_lo, qs, idesc_sp);
+                            else dm::umma_e4m3_lo<true>(t_s, k_lo + hh * kSub + 2 * k, qs + hh * kSubQ + 2 * k, idesc_sp);
+                        }
                     }
-                }
 #pragma unroll
-                for (int hh = 0; hh < kDH; ++hh) {
+                    for (int hh = 0; hh < kDH; ++hh) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_dp, v_lo, dos, idesc_sp);
-                        else dm::umma_e4m3_lo<true>(t_dp, v_lo + hh * kSub + 2 * k, dos + hh * kSubQ + 2 * k, idesc_sp);
+                        for (int k = 0; k < 4; ++k) {
+                            if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_dp, v_lo, dos, idesc_sp);
+                            else dm::umma_e4m3_lo<true>(t_dp, v_lo + hh * kSub + 2 * k, dos + hh * kSubQ + 2 * k, idesc_sp);
+                        }
                     }
+                    dm::umma_commit(&s.bar_sp_full[b]);
                 }
-                dm::umma_commit(&s.bar_sp_full[b]);
-            };
-            auto issue_dkv = [&](int it) {
-                const int st = it % kStages, par = (m_lo + it) & 1, pp = ((m_lo + it) >> 1) & 1;
+                __syncwarp();
+            }
+        } else if (warp == 9) {
+            // ---- dV_tmp (+)= P-hat8^T dO8 and dK_tmp = dS'8^T Q8 once the codes of m-block `it` are in shared memory; the
+            // finished dS' tile of a row pair leaves by one TMA store
+            constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
+            constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;
+            const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
+            const uint32_t pt_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.pt)), ds_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.ds[0]));
+            const int ds_row0 = (int)((((int64_t)bhl * nq_blk + (m_lo >> 1)) * nbn + J) * 128);   // dS' tile of the first row pair
+            for (int it = 0; it < n_it; ++it) {
+                const int st = it % kStages, par = it & 1, pp = (it >> 1) & 1;
                 dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
+                // every compute warp is past the row constants of this m-block: their ring slot may be refilled
+                if (leader) dm::mbar_arrive(&s.bar_rows_free[it % 3]);
                 if (it >= 1) dm::mbar_wait(&s.bar_dkv_free, (it - 1) & 1, wc);
                 dm::tc_fence_after();
                 const uint32_t qs = q_lo + st * kStageQ + zh * kSubQ, dos = do_lo + st * kStageQ + zh * kSubQ;
                 const uint32_t pa = pt_lo + 4 * par, da = ds_lo + pp * kSub + 4 * par;
-                // head_dim 128: dV_tmp accumulates the two m-blocks of a 128-row dO scale block; head_dim 256: one m-block
-                dm::umma_e4m3_lo_rt(t_dv, pa, dos, idesc_dkv, (kD == 128 && par != 0) ? 1u : 0u);
-                dm::umma_e4m3_lo<true>(t_dv, pa + 2, dos + 256, idesc_dkv);
-                dm::umma_e4m3_lo<false>(t_dk, da, qs, idesc_dkv);
-                dm::umma_e4m3_lo<true>(t_dk, da + 2, qs + 256, idesc_dkv);
-                dm::umma_commit(&s.bar_dkv_full);
-                if (par == 1 && zh == 0) {   // the pair's 128 x 128 dS' tile is complete: one TMA store to the workspace
-                    dm::tma_store_2d(&tm_ds, 0, ds_row0 + ((it + (m_lo & 1)) >> 1) * (nbn * 128), s.ds[pp]);
-                    dm::tma_store_commit();
+                if (leader) {
+                    // head_dim 128: dV_tmp accumulates the two m-blocks of a 128-row dO scale block; head_dim 256: one m-block
+                    dm::umma_e4m3_lo_rt(t_dv, pa, dos, idesc_dkv, (kD == 128 && par != 0) ? 1u : 0u);
+                    dm::umma_e4m3_lo<true>(t_dv, pa + 2, dos + 256, idesc_dkv);
+                    dm::umma_e4m3_lo<false>(t_dk, da, qs, idesc_dkv);
+                    dm::umma_e4m3_lo<true>(t_dk, da + 2, qs + 256, idesc_dkv);
+                    dm::umma_commit(&s.bar_dkv_full);
+                    dm::umma_commit(&s.bar_stage_free[st]);      // the Q / dO stage has been read for the last time
+                    if (par == 1 && zh == 0) {
+                        dm::tma_store_2d(&tm_ds, 0, ds_row0 + (it >> 1) * (nbn * 128), s.ds[pp]);
+                        dm::tma_store_commit();
+                        dm::tma_store_wait_read0();
+                        dm::mbar_arrive(&s.bar_ds_free[pp]);
+                    }
                 }
-            };
-            dm::mbar_expect_tx(&s.bar_kv, 2 * kDH * kTile);
-            for (int hh = 0; hh < kDH; ++hh) {
-                dm::tma_load_2d(s.k[hh], &tm_k, 128 * hh, kv_row0, &s.bar_kv);
-                dm::tma_load_2d(s.v[hh], &tm_v, 128 * hh, kv_row0, &s.bar_kv);
+                __syncwarp();
             }
-            for (int i = 0; i < kStages && i < n_it; ++i) load_qdo(i);
-            dm::mbar_wait(&s.bar_kv, 0, wc);
-            issue_sp(0);
-            if (n_it > 1) issue_sp(1);
+            if (n_it > 0) {
+                // the last products: wait so shared memory stays valid until the tensor pipe has read it
+                dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
+                if (leader) dm::tma_store_wait_all0();
+            }
+        } else if (warp == 10) {
+            // ---- TMA loads: K / V once, then the Q8 / dO8 tiles of the m-blocks as far ahead as the ring allows
+            const int q_row0 = hc.bh * p.rm.nq + m_lo * 64;
+            if (n_it > 0 && leader) {
+                dm::mbar_expect_tx(&s.bar_kv, 2 * kDH * kTile);
+                for (int hh = 0; hh < kDH; ++hh) {
+                    dm::tma_load_2d(s.k[hh], &tm_k, 128 * hh, kv_row0, &s.bar_kv);
+                    dm::tma_load_2d(s.v[hh], &tm_v, 128 * hh, kv_row0, &s.bar_kv);
+                }
+            }
             for (int it = 0; it < n_it; ++it) {
-                issue_dkv(it);
-                // the Q / dO stage of m-block it - 1 is free once its dK / dV products have completed; the compute warps
-                // have waited for exactly that before they released the product buffers for m-block `it`
-                if (it >= 1 && it - 1 + kStages < n_it) load_qdo(it - 1 + kStages);
-                // m-block it + 2 may rewrite the dS' tile that a store issued two m-blocks ago is draining: S / dP of that
-                // m-block, which gate the compute warps, are issued only once the store has read shared memory
-                dm::tma_store_wait_read0();
-                if (it + 2 < n_it) issue_sp(it + 2);
+                const int st = it % kStages;
+                if (it >= kStages) dm::mbar_wait(&s.bar_stage_free[st], (it / kStages - 1) & 1, wc);
+                if (leader) {
+                    dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
+#pragma unroll
+                    for (int hh = 0; hh < kDH; ++hh) {
+                        dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
+                        dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
+                    }
+                }
+                __syncwarp();
             }
-            // the last products: wait so shared memory stays valid until the tensor pipe has read it
-            dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
-            dm::tma_store_wait_all0();
+        } else {
+            // ---- per-row constants of the m-blocks, three ahead: 8 - lse * log2e and delta * k8s(group) for the 64 rows
+            // (two per lane), and the Q / dO scales of the m-block
+            const int nsq = kD == 128 ? nq_blk : nbm;
+            float kk[kGrp];
+#pragma unroll
+            for (int gq = 0; gq < kGrp; ++gq) kk[gq] = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + gq];
+            for (int it = 0; it < n_it; ++it) {
+                const int slot = it % 3, mb = m_lo + it;
+                const int64_t gi = (int64_t)hc.bh * p.rm.nq + (int64_t)mb * 64 + 2 * lane;
+                const float2 l2 = *reinterpret_cast<const float2*>(p.lse + gi);
+                const float2 d2 = *reinterpret_cast<const float2*>(p.delta + gi);
+                const int sq = (int)((int64_t)hc.bh * nsq) + (kD == 128 ? (mb >> 1) : mb);
+                const float sc_v = lane == 0 ? p.q8s[sq] : (lane == 1 ? p.do8s[sq] : 0.f);
+                if (it >= 3) dm::mbar_wait(&s.bar_rows_free[slot], (it / 3 - 1) & 1, wc);
+                *reinterpret_cast<float2*>(&s.rc[slot][2 * lane]) = make_float2(dm::phat_row_const(l2.x), dm::phat_row_const(l2.y));
+#pragma unroll
+                for (int gq = 0; gq < kGrp; ++gq)
+                    *reinterpret_cast<float2*>(&s.dlk[slot][gq][2 * lane]) = make_float2(d2.x * kk[gq], d2.y * kk[gq]);
+                if (lane < 2) s.sc[slot][lane] = sc_v;
+                __syncwarp();
+                if (leader) dm::mbar_arrive(&s.bar_rows_full[slot]);
+            }
         }
     } else {
         // =============================================================== compute warps
@@ -227,8 +282,6 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
         const int kgrp = key / kKPS;                  // K / V scale group inside the block
         const int khalf = key >> 6;                   // 64-key half (the psi tile at head_dim 256)
-        const int nsq = kD == 128 ? nq_blk : nbm;     // Q / dO scale blocks per head
-        auto sq_idx = [&](int mb_) { return kD == 128 ? (mb_ >> 1) : mb_; };
         const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
         const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
@@ -239,34 +292,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
         for (int i = 0; i < 64; ++i) { dk_acc[i] = 0.f; dv_acc[i] = 0.f; }
 
-        // Per-row constants (8 - lse * log2e, delta * k8s(group)) travel two m-blocks ahead: fetched into registers by
-        // threads 0..127 (row = tid & 63, scale group = tid >> 6), parked in a 3-deep shared-memory ring after the amax
-        // barrier of the current m-block; the amax barrier of the next m-block orders the ring for its readers.
-        const int rc_r = tid & 63, rc_grp = (tid >> 6) & (kGrp - 1);
-        const float rc_kk = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + rc_grp];
-        auto fetch_rows = [&](int it, float& lse_v, float& dl_v) {
-            if (tid < 64 * kGrp && it < n_it) {
-                const int64_t gi = (int64_t)hc.bh * p.rm.nq + (int64_t)(m_lo + it) * 64 + rc_r;
-                lse_v = p.lse[gi];
-                dl_v = p.delta[gi];
-            }
-        };
-        auto park_rows = [&](int it, float lse_v, float dl_v) {
-            if (tid < 64 * kGrp && it < n_it) {
-                s.dlk[it % 3][rc_grp][rc_r] = dl_v * rc_kk;
-                if (rc_grp == 0) s.rc[it % 3][rc_r] = dm::phat_row_const(lse_v);
-            }
-        };
-        float lse_n = 0.f, dl_n = 0.f;
-        fetch_rows(0, lse_n, dl_n);
-        park_rows(0, lse_n, dl_n);
-        fetch_rows(1, lse_n, dl_n);
-        park_rows(1, lse_n, dl_n);
-        fetch_rows(2, lse_n, dl_n);                    // parked during iteration 0
-        float q8sc_n = n_it > 0 ? p.q8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)] : 0.f;
-        float do8sc_n = n_it > 0 ? p.do8s[(int64_t)hc.bh * nsq + sq_idx(m_lo)] : 0.f;
         float g_prev = 0.f, f_prev = 0.f;
-        dm::named_bar_sync(1, kComputeThreads);
 
         auto fold = [&](int it, float g_fold, float f_fold) {
             dm::mbar_wait(&s.bar_dkv_full, it & 1, wc);
@@ -290,15 +316,12 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
         for (int it = 0; it < n_it; ++it) {
             const int mb = m_lo + it, par = mb & 1, sb = it & 1, rb = it % 3;
-            const float q8sc = q8sc_n, do8sc = do8sc_n;
-            if (it + 1 < n_it) {
-                q8sc_n = p.q8s[(int64_t)hc.bh * nsq + sq_idx(mb + 1)];
-                do8sc_n = p.do8s[(int64_t)hc.bh * nsq + sq_idx(mb + 1)];
-            }
-            const float dsc = dm::descale_log2(q8sc, k8s_t);
-            const float dpk = do8sc * v8s_t * k8s_t;
             dm::mbar_wait(&s.bar_sp_full[sb], (it >> 1) & 1, wc);
             dm::tc_fence_after();
+            // the ring slot of this m-block's row constants and scales was complete before S^T / dP^T were issued
+            const float q8sc = s.sc[rb][0], do8sc = s.sc[rb][1];
+            const float dsc = dm::descale_log2(q8sc, k8s_t);
+            const float dpk = do8sc * v8s_t * k8s_t;
 
             // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory.  S^T first: the exponentials run while
             // dP^T is still on its way from tensor memory.
@@ -372,8 +395,6 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 const int w0 = 2 * khalf;
                 amax = fmaxf(fmaxf(s.amax[sb][w0], s.amax[sb][w0 + 1]), fmaxf(s.amax[sb][w0 + 4], s.amax[sb][w0 + 5]));
             }
-            park_rows(it + 2, lse_n, dl_n);
-            fetch_rows(it + 3, lse_n, dl_n);
             const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
             const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
             // psi = max(psi_raw, g_max * 256e-8 / q8sc); the quotient can only win when its numerator exceeds
@@ -398,7 +419,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
             // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2; the previous m-block's
             // dK product keeps arriving in 16-column chunks between the halves
-            uint8_t* dst = s.ds[(mb >> 1) & 1];
+            uint8_t* dst = s.ds[(it >> 1) & 1];       // m_lo is even: it >> 1 counts this CTA's row pairs
             {
                 uint32_t w[4];
 #pragma unroll
