@@ -204,7 +204,7 @@ def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=
     """O (B, N, H, D) bf16 and LSE [B*H, N] fp32; with a head range only those heads are written.  With a row map `cp`
     (sequence split) Q8 holds the rank's nq local rows, K8 / V8 the whole sequence, and O / LSE are local."""
     BH, nq, D = Q8.shape
-    N = K8.shape[1]
+    N = nq if cp is None else K8.shape[1]      # whole sequence: the Q-side tensors carry it
     hcount = H if hcount is None else hcount
     dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
@@ -224,7 +224,7 @@ def fwd_fp8(Q8, K8, V8, Q8s, K8s, V8s, B, H, Hk, causal, h0=0, hcount=None, out=
 
 def delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, h0=0, hcount=None, out=None, cp=None):
     BH, nq, D = Q8.shape
-    N = K8.shape[1]
+    N = nq if cp is None else K8.shape[1]      # whole sequence: the Q-side tensors carry it
     hcount = H if hcount is None else hcount
     dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):
@@ -254,7 +254,7 @@ def bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal
     """dK, dV (B, N, H, D) per query head (bf16, or fp32 partials with out_fp32) plus the dS' / psi workspace for pass 2.
     With a row map `cp` the Q-side inputs and the workspace hold the rank's local rows; dK / dV span the whole sequence."""
     BH, nq, D = Q8.shape
-    N = K8.shape[1]
+    N = nq if cp is None else K8.shape[1]      # whole sequence: the Q-side tensors carry it
     hcount = H if hcount is None else hcount
     dev = _device_of(Q8, K8, V8)
     with torch.cuda.device(dev):

@@ -2,34 +2,39 @@
 // faithful P basis (per row, per 64-key group) -- csrc/softmax_fq8f.h and csrc/mainloop_fwd_sm90_fp8f.hpp of the
 // reference, restated for tcgen05.
 //
-// One CTA = 128 query rows of one (batch, head); 256 threads.  Key tiles of 128 keys (two 64-key groups) are visited
-// from the diagonal tile downwards.  Per tile:
-//   S = Q K^T            4 x tcgen05.mma (M128 N128 K32), accumulator in tensor memory columns [0, 128)
+// One CTA = 128 query rows of one (batch, head).  384 threads: warps 0..7 compute, warps 8..10 are service warps (one
+// issuing lane each, loops converged): warp 8 issues S, warp 9 issues the P V products, warp 10 the TMA loads.  Key tiles
+// of 128 keys (two 64-key groups) are visited from the diagonal tile downwards.  Per tile:
+//   S = Q K^T            4 x tcgen05.mma (M128 N128 K32) into one of two tensor-memory buffers, up to two tiles ahead
 //   softmax              thread (quarter q, lane, warpgroup g) owns row 32q+lane and key group g: group max, running max
 //                        exchanged through shared memory, basis ms_g = max(gm_g*l2, m*l2 - 12) - log2(448),
-//                        codes = e4m3(2^(S*l2 - ms_g)) written to a swizzled K-major tile; the denominator is summed
-//                        from the unrounded p
-//   D_g = C_g V_g        2 x tcgen05.mma per group into zero-initialised tensor-memory temporaries [128,256), [256,384)
-//   O += D_g * w_g       w_g = v8sc_g * 2^(ms_g - m*l2); O lives in registers (64 columns per thread) so the
-//                        cross-tile rescale by alpha is a register multiply
-// K / V tiles arrive by TMA into a 2-stage ring; the S MMA of the next tile is issued as soon as S has been read, so
-// the tensor pipe works under the softmax arithmetic.  Every mbarrier wait is bounded.
+//                        codes = e4m3(2^(S*l2 - ms_g)) written to one of two swizzled K-major tiles; the denominator is
+//                        summed from the unrounded p
+//   D_g = C_g V_g        2 x tcgen05.mma per group into zero-initialised tensor-memory temporaries, issued when the codes
+//                        are in shared memory; they run under the next tile's softmax
+//   O += D_g * w_g       w_g = v8sc_g * 2^(ms_g - m*l2), one tile late; O lives in registers (64 columns per thread) so
+//                        the cross-tile rescale by alpha is a register multiply.  The order of the arithmetic on O is
+//                        that of the straight loop: ... * alpha(t), + D(t) w(t), * alpha(t+1), ...
+// K / V tiles arrive by TMA into a 3-stage ring.  Every mbarrier wait is bounded.
 #include "dm_attn_common.cuh"
 #include "dm_host.h"
 
 namespace {
 
 constexpr int kTile = 128 * 128;   // bytes of one e4m3 tile (128 rows x 128 bytes)
+constexpr int kStages = 3;
+constexpr int kThreads = 384;
+constexpr int kComputeThreads = 256;
 
 struct FwdSmem {
     alignas(1024) uint8_t q[kTile];
-    alignas(1024) uint8_t k[2][kTile];
-    alignas(1024) uint8_t v[2][kTile];
-    alignas(1024) uint8_t p[kTile];
-    float gmax[2][128];
-    float wgt[2][128];
+    alignas(1024) uint8_t k[kStages][kTile];
+    alignas(1024) uint8_t v[kStages][kTile];
+    alignas(1024) uint8_t p[2][kTile];
+    float gmax[2][2][128];            // [tile parity][key group][row]
+    float wgt[2][2][128];
     float lsum[2][128];
-    uint64_t bar_q, bar_kv[2], bar_s, bar_d[2];
+    uint64_t bar_q, bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2], bar_d_full;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -45,14 +50,12 @@ struct FwdParams {
     dm::RowMap rm;
 };
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     FwdSmem& s = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = warp >> 2;                  // warpgroup = key group inside the tile, and the 64-column half of O
-    const int row = (warp & 3) * 32 + lane;   // query row inside the block = tensor-memory lane
     const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
     const int nblk = p.N / 128;
     const int nq_blk = p.rm.nq / 128;
@@ -64,11 +67,16 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (tid == 0) {
         s.abort_flag = 0;
         dm::mbar_init(&s.bar_q, 1);
-        dm::mbar_init(&s.bar_kv[0], 1);
-        dm::mbar_init(&s.bar_kv[1], 1);
-        dm::mbar_init(&s.bar_s, 1);
-        dm::mbar_init(&s.bar_d[0], 1);
-        dm::mbar_init(&s.bar_d[1], 1);
+        for (int i = 0; i < kStages; ++i) {
+            dm::mbar_init(&s.bar_kv[i], 1);
+            dm::mbar_init(&s.bar_kv_free[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            dm::mbar_init(&s.bar_s_full[i], 1);
+            dm::mbar_init(&s.bar_s_free[i], 8);
+            dm::mbar_init(&s.bar_codes[i], 8);
+        }
+        dm::mbar_init(&s.bar_d_full, 1);
         dm::fence_mbar_init();
         dm::tma_prefetch_desc(&tm_q);
         dm::tma_prefetch_desc(&tm_k);
@@ -79,159 +87,204 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncthreads();
     dm::tc_fence_after();
     const uint32_t tmem = s.tmem_base;
-    const uint32_t t_s = tmem, t_d0 = tmem + 128, t_d1 = tmem + 256;
-    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+    const uint32_t t_d0 = tmem + 256, t_d1 = tmem + 384;      // S buffers at columns [0, 128) and [128, 256)
 
-    const int q_row0 = hc.bh * p.rm.nq + li * 128;
-    const int kv_row0 = hc.bhk * p.N;
-    constexpr uint32_t idesc_s = dm::idesc_e4m3(128, 128, false, false);
-    constexpr uint32_t idesc_pv = dm::idesc_e4m3(128, 128, false, true);
-
-    auto load_kv = [&](int it) {   // thread 0 only
-        const int j = n_tiles - 1 - it, st = it & 1;
-        dm::mbar_expect_tx(&s.bar_kv[st], 2 * kTile);
-        dm::tma_load_2d(s.k[st], &tm_k, 0, kv_row0 + j * 128, &s.bar_kv[st]);
-        dm::tma_load_2d(s.v[st], &tm_v, 0, kv_row0 + j * 128, &s.bar_kv[st]);
-    };
-    auto issue_s = [&](int it) {   // thread 0 only: S = Q K^T for iteration `it`
-        const int st = it & 1;
-        dm::mbar_wait(&s.bar_kv[st], (it >> 1) & 1, wc);
-        dm::tc_fence_after();
-        const uint32_t qa = dm::smem_u32(s.q), ka = dm::smem_u32(s.k[st]);
+    if (warp >= 8) {
+        // =============================================================== service warps
+        dm::reg_dec<40>();
+        const bool leader = lane == 0;
+        const int kv_row0 = hc.bhk * p.N;
+        constexpr uint32_t kSub = kTile >> 4;
+        if (warp == 8) {
+            // ---- S = Q K^T of tile `it` into buffer it & 1
+            constexpr uint32_t idesc_s = dm::idesc_e4m3(128, 128, false, false);
+            const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q)), k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0]));
+            dm::mbar_wait(&s.bar_q, 0, wc);
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % kStages, b = it & 1;
+                dm::mbar_wait(&s.bar_kv[st], (it / kStages) & 1, wc);
+                if (it >= 2) dm::mbar_wait(&s.bar_s_free[b], ((it - 2) >> 1) & 1, wc);
+                dm::tc_fence_after();
+                const uint32_t ks = k_lo + st * kSub, ts = tmem + b * 128;
+                if (leader) {
+                    dm::umma_e4m3_lo<false>(ts, q_lo, ks, idesc_s);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            dm::umma_e4m3(t_s, dm::smem_desc_sw128(qa + 32 * k), dm::smem_desc_sw128(ka + 32 * k), idesc_s, k > 0);
-        dm::umma_commit(&s.bar_s);
-    };
-
-    if (tid == 0) {
-        dm::mbar_expect_tx(&s.bar_q, kTile);
-        dm::tma_load_2d(s.q, &tm_q, 0, q_row0, &s.bar_q);
-        load_kv(0);
-        if (n_tiles > 1) load_kv(1);
-        dm::mbar_wait(&s.bar_q, 0, wc);
-        issue_s(0);
-    }
-
-    const float q8sc = p.q8s[(int64_t)hc.bh * nq_blk + li];
-    float m_run = -INFINITY, l_part = 0.f;
-    float o_acc[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o_acc[i] = 0.f;
-
-    for (int it = 0; it < n_tiles; ++it) {
-        const int j = n_tiles - 1 - it, st = it & 1;
-        const float ks = p.k8s[(int64_t)hc.bhk * (p.N / 64) + 2 * j + g];
-        const float vs = p.v8s[(int64_t)hc.bhk * (p.N / 64) + 2 * j + g];
-
-        // ---- S for this thread's (row, key group): 64 fp32 values
-        dm::mbar_wait(&s.bar_s, it & 1, wc);
-        dm::tc_fence_after();
-        float sv[64];
-        dm::tmem_ld32(dm::tmem_addr(t_s, lane_base, g * 64), reinterpret_cast<uint32_t*>(sv));
-        dm::tmem_ld32(dm::tmem_addr(t_s, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(sv) + 32);
-        dm::tmem_ld_wait();
-        dm::tc_fence_before();
-        __syncthreads();                                   // S columns are free again
-        if (tid == 0 && it + 1 < n_tiles) issue_s(it + 1);
-
-        const float dsc = q8sc * ks;
-        float gm = -INFINITY;
-        if (p.causal && j == I) {
-#pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                sv[c] = (g * 64 + c > row) ? -INFINITY : sv[c] * dsc;
-                gm = fmaxf(gm, sv[c]);
+                    for (int k = 1; k < 4; ++k) dm::umma_e4m3_lo<true>(ts, q_lo + 2 * k, ks + 2 * k, idesc_s);
+                    dm::umma_commit(&s.bar_s_full[b]);
+                }
+                __syncwarp();
             }
-        } else {
-#pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                sv[c] *= dsc;
-                gm = fmaxf(gm, sv[c]);
+        } else if (warp == 9) {
+            // ---- D_g = C_g V_g for both key groups once the codes of tile `it` are in shared memory and the products of
+            // tile it - 1 have been folded (the compute warps arrive on bar_codes after both)
+            constexpr uint32_t idesc_pv = dm::idesc_e4m3(128, 128, false, true);
+            const uint32_t p_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.p[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % kStages;
+                dm::mbar_wait(&s.bar_kv[st], (it / kStages) & 1, wc);
+                dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
+                dm::tc_fence_after();
+                const uint32_t pa = p_lo + (it & 1) * kSub, va = v_lo + st * kSub;
+                if (leader) {
+                    // group gg: codes columns [64 gg, 64 gg + 64) (K-major, +4 per 64 bytes), V rows [64 gg, +64) (MN-major, +512)
+                    dm::umma_e4m3_lo<false>(t_d0, pa, va, idesc_pv);
+                    dm::umma_e4m3_lo<true>(t_d0, pa + 2, va + 256, idesc_pv);
+                    dm::umma_e4m3_lo<false>(t_d1, pa + 4, va + 512, idesc_pv);
+                    dm::umma_e4m3_lo<true>(t_d1, pa + 6, va + 768, idesc_pv);
+                    dm::umma_commit(&s.bar_d_full);
+                    dm::umma_commit(&s.bar_kv_free[st]);       // K was read by S long ago, V just now
+                }
+                __syncwarp();
+            }
+        } else if (warp == 10) {
+            // ---- TMA loads: Q once, K / V tiles as far ahead as the ring allows
+            const int q_row0 = hc.bh * p.rm.nq + li * 128;
+            if (leader) {
+                dm::mbar_expect_tx(&s.bar_q, kTile);
+                dm::tma_load_2d(s.q, &tm_q, 0, q_row0, &s.bar_q);
+            }
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % kStages, j = n_tiles - 1 - it;
+                if (it >= kStages) dm::mbar_wait(&s.bar_kv_free[st], (it / kStages - 1) & 1, wc);
+                if (leader) {
+                    dm::mbar_expect_tx(&s.bar_kv[st], 2 * kTile);
+                    dm::tma_load_2d(s.k[st], &tm_k, 0, kv_row0 + j * 128, &s.bar_kv[st]);
+                    dm::tma_load_2d(s.v[st], &tm_v, 0, kv_row0 + j * 128, &s.bar_kv[st]);
+                }
+                __syncwarp();
             }
         }
-        s.gmax[g][row] = gm;
-        __syncthreads();
-        const float tile_max = fmaxf(s.gmax[0][row], s.gmax[1][row]);
-        const float m_new = fmaxf(m_run, tile_max);
-        const float m_cur = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = dm::ex2((m_run - m_cur) * dm::kLog2e);
-        const float ml2 = m_cur * dm::kLog2e;
-        const float ms = fmaxf(gm * dm::kLog2e, ml2 - dm::kPhatFloorB) - dm::kLog2_448;
-        float part = 0.f;
-        uint32_t codes[16];
+    } else {
+        // =============================================================== compute warps
+        dm::reg_inc<232>();
+        const int g = warp >> 2;                  // warpgroup = key group inside the tile, and the 64-column half of O
+        const int row = (warp & 3) * 32 + lane;   // query row inside the block = tensor-memory lane
+        const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+        const float q8sc = p.q8s[(int64_t)hc.bh * nq_blk + li];
+        const float* ksp = p.k8s + (int64_t)hc.bhk * (p.N / 64) + g;
+        const float* vsp = p.v8s + (int64_t)hc.bhk * (p.N / 64) + g;
+        float m_run = -INFINITY, l_part = 0.f;
+        float o_acc[64];
 #pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-            const float p0 = dm::ex2(fmaf(sv[c], dm::kLog2e, -ms));
-            const float p1 = dm::ex2(fmaf(sv[c + 1], dm::kLog2e, -ms));
-            const float p2 = dm::ex2(fmaf(sv[c + 2], dm::kLog2e, -ms));
-            const float p3 = dm::ex2(fmaf(sv[c + 3], dm::kLog2e, -ms));
-            part += (p0 + p1) + (p2 + p3);
-            codes[c >> 2] = dm::cvt_e4m3x4(p0, p1, p2, p3);
-        }
-        const float sigma = dm::ex2(ms - ml2);
-        l_part = fmaf(l_part, alpha, sigma * part);
-        s.wgt[g][row] = vs * sigma;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(s.p + dm::sw128(row, g * 64 + c * 16)) =
-                make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
-#pragma unroll
-        for (int i = 0; i < 64; ++i) o_acc[i] *= alpha;
-        m_run = m_new;
-        dm::fence_proxy_async_smem();
-        dm::tc_fence_before();
-        __syncthreads();                                   // P codes and weights are visible
+        for (int i = 0; i < 64; ++i) o_acc[i] = 0.f;
 
-        if (tid == 0) {
+        // the products of tile `t` into O: both groups' 64 columns of this thread, 16 at a time
+        auto fold = [&](int t) {
+            dm::mbar_wait(&s.bar_d_full, t & 1, wc);
             dm::tc_fence_after();
-            const uint32_t pa = dm::smem_u32(s.p), va = dm::smem_u32(s.v[st]);
 #pragma unroll
             for (int gg = 0; gg < 2; ++gg) {
+                const float w = s.wgt[t & 1][gg][row];
+                const uint32_t td = gg ? t_d1 : t_d0;
+                uint32_t stage[32];
 #pragma unroll
-                for (int k = 0; k < 2; ++k)
-                    dm::umma_e4m3(gg ? t_d1 : t_d0, dm::smem_desc_sw128(pa + 64 * gg + 32 * k),
-                                  dm::smem_desc_sw128(va + 8192 * gg + 4096 * k), idesc_pv, k > 0);
-                dm::umma_commit(&s.bar_d[gg]);
+                for (int h = 0; h < 2; ++h) {
+                    dm::tmem_ld32(dm::tmem_addr(td, lane_base, g * 64 + 32 * h), stage);
+                    dm::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o_acc[32 * h + i] = fmaf(__uint_as_float(stage[i]), w, o_acc[32 * h + i]);
+                }
             }
-        }
-        // ---- fold the two group products into O (this thread: row, columns [64 g, 64 g + 64))
-#pragma unroll
-        for (int gg = 0; gg < 2; ++gg) {
-            dm::mbar_wait(&s.bar_d[gg], it & 1, wc);
-            dm::tc_fence_after();
-            const float w = s.wgt[gg][row];
-            float dv[64];
-            dm::tmem_ld32(dm::tmem_addr(gg ? t_d1 : t_d0, lane_base, g * 64), reinterpret_cast<uint32_t*>(dv));
-            dm::tmem_ld32(dm::tmem_addr(gg ? t_d1 : t_d0, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(dv) + 32);
-            dm::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 64; ++i) o_acc[i] = fmaf(dv[i], w, o_acc[i]);
-        }
-        dm::tc_fence_before();
-        // both PV products are complete: this stage's K / V tiles are free
-        if (tid == 0 && it + 2 < n_tiles) load_kv(it + 2);
-    }
+            dm::tc_fence_before();
+        };
 
-    // ---- epilogue
-    s.lsum[g][row] = l_part;
-    __syncthreads();
-    const float l = s.lsum[0][row] + s.lsum[1][row];
-    const bool dead = (l == 0.f) || (l != l);
-    const float inv = dead ? 0.f : 1.0f / l;
-    const int n_glob = li * 128 + row;          // row inside the (local) Q-side tensors
-    __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128 + g * 64;
+        float ks_n = ksp[2 * (n_tiles - 1)], vs_n = vsp[2 * (n_tiles - 1)];
+        for (int it = 0; it < n_tiles; ++it) {
+            const int j = n_tiles - 1 - it, b = it & 1;
+            const float ks = ks_n, vs = vs_n;
+            if (it + 1 < n_tiles) {
+                ks_n = ksp[2 * (j - 1)];
+                vs_n = vsp[2 * (j - 1)];
+            }
+
+            // ---- S for this thread's (row, key group): 64 fp32 values
+            dm::mbar_wait(&s.bar_s_full[b], (it >> 1) & 1, wc);
+            dm::tc_fence_after();
+            float sv[64];
+            dm::tmem_ld32(dm::tmem_addr(tmem + b * 128, lane_base, g * 64), reinterpret_cast<uint32_t*>(sv));
+            dm::tmem_ld32(dm::tmem_addr(tmem + b * 128, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(sv) + 32);
+            dm::tmem_ld_wait();
+            dm::tc_fence_before();
+            dm::mbar_arrive_warp(&s.bar_s_free[b]);            // this S buffer may be overwritten
+
+            const float dsc = q8sc * ks;
+            float gm = -INFINITY;
+            if (p.causal && j == I) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        uint32_t w4[4];
+                for (int c = 0; c < 64; ++c) {
+                    sv[c] = (g * 64 + c > row) ? -INFINITY : sv[c] * dsc;
+                    gm = fmaxf(gm, sv[c]);
+                }
+            } else {
+                float gm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
-            w4[e] = *reinterpret_cast<uint32_t*>(&t);
+                for (int c = 0; c < 64; ++c) {
+                    sv[c] *= dsc;
+                    gm4[c & 3] = fmaxf(gm4[c & 3], sv[c]);
+                }
+                gm = fmaxf(fmaxf(gm4[0], gm4[1]), fmaxf(gm4[2], gm4[3]));
+            }
+            s.gmax[b][g][row] = gm;
+            dm::named_bar_sync(1, kComputeThreads);
+            const float tile_max = fmaxf(s.gmax[b][0][row], s.gmax[b][1][row]);
+            const float m_new = fmaxf(m_run, tile_max);
+            const float m_cur = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = dm::ex2((m_run - m_cur) * dm::kLog2e);
+            const float ml2 = m_cur * dm::kLog2e;
+            const float ms = fmaxf(gm * dm::kLog2e, ml2 - dm::kPhatFloorB) - dm::kLog2_448;
+            float part = 0.f;
+            uint32_t codes[16];
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+                const float p0 = dm::ex2(fmaf(sv[c], dm::kLog2e, -ms));
+                const float p1 = dm::ex2(fmaf(sv[c + 1], dm::kLog2e, -ms));
+                const float p2 = dm::ex2(fmaf(sv[c + 2], dm::kLog2e, -ms));
+                const float p3 = dm::ex2(fmaf(sv[c + 3], dm::kLog2e, -ms));
+                part += (p0 + p1) + (p2 + p3);
+                codes[c >> 2] = dm::cvt_e4m3x4(p0, p1, p2, p3);
+            }
+            const float sigma = dm::ex2(ms - ml2);
+            l_part = fmaf(l_part, alpha, sigma * part);
+            s.wgt[b][g][row] = vs * sigma;
+            // the tile of parity b was last read by the products of tile it - 2, folded one iteration ago
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(s.p[b] + dm::sw128(row, g * 64 + c * 16)) =
+                    make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
+            dm::fence_proxy_async_smem();
+            // ---- the previous tile's products, complete by now, then this tile's rescale
+            if (it > 0) fold(it - 1);
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) o_acc[i] *= alpha;
+            }
+            m_run = m_new;
+            dm::mbar_arrive_warp(&s.bar_codes[b]);
         }
-        reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        dm::named_bar_sync(1, kComputeThreads);          // the other warpgroup's weight of the last tile
+        fold(n_tiles - 1);
+
+        // ---- epilogue
+        s.lsum[g][row] = l_part;
+        dm::named_bar_sync(1, kComputeThreads);
+        const float l = s.lsum[0][row] + s.lsum[1][row];
+        const bool dead = (l == 0.f) || (l != l);
+        const float inv = dead ? 0.f : 1.0f / l;
+        const int n_glob = li * 128 + row;          // row inside the (local) Q-side tensors
+        __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128 + g * 64;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
+                w4[e] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
+        if (g == 0) p.lse[(int64_t)hc.bh * p.rm.nq + n_glob] = dead ? -INFINITY : m_run + logf(l);
     }
-    if (g == 0) p.lse[(int64_t)hc.bh * p.rm.nq + n_glob] = dead ? -INFINITY : m_run + logf(l);
+    dm::tc_fence_before();
     __syncthreads();
     if (warp == 0) dm::tmem_dealloc(tmem, 512);
 }
@@ -316,7 +369,7 @@ extern "C" int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, con
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    fwd_d128_kernel<<<dim3(cp.nq / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+    fwd_d128_kernel<<<dim3(cp.nq / 128, sh.B * hcount), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
