@@ -57,7 +57,7 @@ struct Bwd1Smem {
     alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]; an m-block owns one 64-byte half
     alignas(1024) uint8_t ds[2][kTile];   // dS' codes, same layout, one tile per 128-row pair parity (a TMA store drains the other)
     alignas(16) float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
-    alignas(16) float dlk[3][kGrp][64];               // delta * k8s(group) per row
+    alignas(16) float dlk[3][kGrp][64];               // -delta * k8s(group) per row
     float sc[3][2];                                   // q8sc, do8sc of the m-block (same ring)
     float amax[2][8];
     uint64_t bar_kv, bar_qdo[kStages], bar_stage_free[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full,
@@ -269,7 +269,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 *reinterpret_cast<float2*>(&s.rc[slot][2 * lane]) = make_float2(dm::phat_row_const(l2.x), dm::phat_row_const(l2.y));
 #pragma unroll
                 for (int gq = 0; gq < kGrp; ++gq)
-                    *reinterpret_cast<float2*>(&s.dlk[slot][gq][2 * lane]) = make_float2(d2.x * kk[gq], d2.y * kk[gq]);
+                    *reinterpret_cast<float2*>(&s.dlk[slot][gq][2 * lane]) = make_float2(-(d2.x * kk[gq]), -(d2.y * kk[gq]));
                 if (lane < 2) s.sc[slot][lane] = sc_v;
                 __syncwarp();
                 if (leader) dm::mbar_arrive(&s.bar_rows_full[slot]);
@@ -334,16 +334,18 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 32]);
             const float4* dl4 = reinterpret_cast<const float4*>(&s.dlk[rb][kgrp][g * 32]);
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
+            for (int c4 = 0; c4 < 8; ++c4) {                // P-hat = 2^min(S dsc + rc, 12), the exponent two at a time
                 const float4 r4 = rc4[c4];
-                const float rcv[4] = {r4.x, r4.y, r4.z, r4.w};
+                const int c = 4 * c4;
+                dm::fma2(sv[c], sv[c + 1], sv[c], sv[c + 1], dsc, r4.x, r4.y);
+                dm::fma2(sv[c + 2], sv[c + 3], sv[c + 2], sv[c + 3], dsc, r4.z, r4.w);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = 4 * c4 + e;
-                    float ph = dm::phat(sv[c], dsc, rcv[e]);
-                    if (diag && key > row_in_pair + c) ph = 0.f;
-                    sv[c] = ph;
-                }
+                for (int e = 0; e < 4; ++e) sv[c + e] = dm::ex2(fminf(sv[c + e], dm::kMoE + 4.0f));
+            }
+            if (diag) {                                     // the diagonal 128 x 128 block only: keys above the row
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (key > row_in_pair + c) sv[c] = 0.f;
             }
             dm::tmem_ld_wait();
             dm::tc_fence_before();
@@ -351,14 +353,14 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
-                const float4 d4 = dl4[c4];
-                const float dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+                const float4 d4 = dl4[c4];                  // -delta * k8s per row
+                const int c = 4 * c4;
+                dm::fma2(ds[c], ds[c + 1], ds[c], ds[c + 1], dpk, d4.x, d4.y);
+                dm::fma2(ds[c + 2], ds[c + 3], ds[c + 2], ds[c + 3], dpk, d4.z, d4.w);
+                dm::mul2(ds[c], ds[c + 1], ds[c], ds[c + 1], sv[c], sv[c + 1]);
+                dm::mul2(ds[c + 2], ds[c + 3], ds[c + 2], ds[c + 3], sv[c + 2], sv[c + 3]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = 4 * c4 + e;
-                    ds[c] = sv[c] * (ds[c] * dpk - dlv[e]);
-                    am4[e] = fmaxf(am4[e], fabsf(ds[c]));
-                }
+                for (int e = 0; e < 4; ++e) am4[e] = fmaxf(am4[e], fabsf(ds[c + e]));
             }
             float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
             {
@@ -379,8 +381,9 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #define DM_FOLD_CHUNK(ACC, SCALE, OFF)                                                                           \
             {                                                                                                    \
                 dm::tmem_ld_wait();                                                                              \
-                _Pragma("unroll") for (int i = 0; i < 16; ++i)                                                   \
-                    ACC[(OFF) + i] = fmaf(__uint_as_float(stage[i]), SCALE, ACC[(OFF) + i]);                     \
+                _Pragma("unroll") for (int i = 0; i < 16; i += 2)                                                \
+                    dm::fma2(ACC[(OFF) + i], ACC[(OFF) + i + 1], __uint_as_float(stage[i]), __uint_as_float(stage[i + 1]), SCALE, \
+                             ACC[(OFF) + i], ACC[(OFF) + i + 1]);                                                \
             }
             if (it > 0) {
                 dm::mbar_wait(&s.bar_dkv_full, (it - 1) & 1, wc);
@@ -423,8 +426,12 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             {
                 uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    w[c] = dm::cvt_e4m3x4(ds[4 * c] * psi_inv, ds[4 * c + 1] * psi_inv, ds[4 * c + 2] * psi_inv, ds[4 * c + 3] * psi_inv);
+                for (int c = 0; c < 4; ++c) {
+                    float a0, a1, a2, a3;
+                    dm::mul2(a0, a1, ds[4 * c], ds[4 * c + 1], psi_inv, psi_inv);
+                    dm::mul2(a2, a3, ds[4 * c + 2], ds[4 * c + 3], psi_inv, psi_inv);
+                    w[c] = dm::cvt_e4m3x4(a0, a1, a2, a3);
+                }
                 *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             if (it > 0) {
@@ -434,8 +441,12 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             {
                 uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    w[c] = dm::cvt_e4m3x4(ds[16 + 4 * c] * psi_inv, ds[17 + 4 * c] * psi_inv, ds[18 + 4 * c] * psi_inv, ds[19 + 4 * c] * psi_inv);
+                for (int c = 0; c < 4; ++c) {
+                    float a0, a1, a2, a3;
+                    dm::mul2(a0, a1, ds[16 + 4 * c], ds[17 + 4 * c], psi_inv, psi_inv);
+                    dm::mul2(a2, a3, ds[18 + 4 * c], ds[19 + 4 * c], psi_inv, psi_inv);
+                    w[c] = dm::cvt_e4m3x4(a0, a1, a2, a3);
+                }
                 *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             dm::fence_proxy_async_smem();

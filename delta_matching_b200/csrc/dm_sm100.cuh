@@ -232,6 +232,18 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Packed fp32 pairs (one instruction for two lanes of arithmetic, IEEE round-to-nearest per component, so the results
+// carry the bits of the scalar operations): y = x * m + c, y = x * m, on two values at a time.
+__device__ __forceinline__ void fma2(float& y0, float& y1, float x0, float x1, float m, float c0, float c1) {
+    const float2 r = __ffma2_rn(make_float2(x0, x1), make_float2(m, m), make_float2(c0, c1));
+    y0 = r.x;
+    y1 = r.y;
+}
+__device__ __forceinline__ void mul2(float& y0, float& y1, float x0, float x1, float m0, float m1) {
+    const float2 r = __fmul2_rn(make_float2(x0, x1), make_float2(m0, m1));
+    y0 = r.x;
+    y1 = r.y;
+}
 // two fp32 -> two e4m3 (round-to-nearest-even, saturate-to-finite), lo in bits 0..7
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     uint16_t r;
