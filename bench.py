@@ -271,15 +271,18 @@ def main():
     launches["n"] = 0
     times = []
     with ClockSampler(local) as clk:
+        # each step is bracketed by its own pair of events (the L2 flush between steps stays outside them); the host does
+        # not wait for a step before it enqueues the next, so the events measure the device, not the launch path
+        evs = []
         for _ in range(args.steps):
             flush.fill_(1)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             step()
             e1.record()
-            e1.synchronize()
-            times.append(e0.elapsed_time(e1))
+            evs.append((e0, e1))
         sync_all()
+        times = [a.elapsed_time(b) for a, b in evs]
     n_launch = launches["n"]
     total_ms = sum(times)
     if world > 1:
