@@ -94,11 +94,11 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const int zh = blockIdx.z;                    // d half whose dK / dV columns this CTA keeps (always 0 at head_dim 128)
     Bwd1Smem<kD>& s = *reinterpret_cast<Bwd1Smem<kD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
     const int nbn = p.N / 128;
     const int nq_blk = p.rm.nq / 128, nbm = p.rm.nq / 64;   // local 128-row blocks and 64-row m-blocks
-    const int J = blockIdx.x;                     // key block; J = 0 has the most m-blocks when causal and is launched first
+    const int J = blockIdx.y;                     // key block; J = 0 has the most m-blocks when causal and is launched first
     // m-blocks are counted in the local rows; global position grows with the local index, and both chunks of a row map
     // start on a 128-row pair, so local and global m-block parity agree.  Causal: start at the first local m-block that is
     // not wholly above the diagonal of key block J; a rank may hold none (n_it == 0: dK = dV = 0 for this block).
@@ -571,7 +571,7 @@ extern "C" int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v
             DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             if (dev >= 0 && dev < 64) done[dev] = true;
         }
-        bwd1_kernel<128><<<dim3(sh.N / 128, sh.B * hcount, 1), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
+        bwd1_kernel<128><<<dim3(sh.B * hcount, sh.N / 128, 1), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
     } else {
         const int smem = (int)sizeof(Bwd1Smem<256>) + 1024;
         static bool done[64] = {false};
@@ -581,7 +581,7 @@ extern "C" int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v
             DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             if (dev >= 0 && dev < 64) done[dev] = true;
         }
-        bwd1_kernel<256><<<dim3(sh.N / 128, sh.B * hcount, 2), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
+        bwd1_kernel<256><<<dim3(sh.B * hcount, sh.N / 128, 2), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
     }
     DM_CUDA(cudaGetLastError());
     return DM_OK;

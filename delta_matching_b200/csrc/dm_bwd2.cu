@@ -45,11 +45,11 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
     const int nbn = p.N / 128, nbm = p.N / 64;
     const int nq_blk = p.rm.nq / 128, nbm_l = p.rm.nq / 64;
-    const int rb = nq_blk - 1 - (int)blockIdx.x;       // local row block, longest first
+    const int rb = nq_blk - 1 - (int)blockIdx.y;       // local row block, longest first
     const int n_it = p.causal ? dm::global_block(p.rm, rb) + 1 : nbn;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
@@ -155,10 +155,10 @@ bwd2_d256_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = warp >> 2;                           // d half
     const int row = (warp & 3) * 32 + lane;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
     const int bhl = hc.b * p.hcount + (hc.h - p.h0);
     const int nbn = p.N / 128, nbm = p.N / 64;
-    const int rb = nbn - 1 - (int)blockIdx.x;
+    const int rb = nbn - 1 - (int)blockIdx.y;
     const int n_it = p.causal ? rb + 1 : nbn;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
@@ -291,7 +291,7 @@ extern "C" int dm_bwd_fp8_pass2_cp(const void* ds8_ws, const float* psi_ws, cons
     if (sh.D == 256) {
         const int smem = (int)sizeof(Bwd2Smem256) + 1024;
         DM_CUDA(cudaFuncSetAttribute(bwd2_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        bwd2_d256_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
+        bwd2_d256_kernel<<<dim3(sh.B * hcount, sh.N / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
         DM_CUDA(cudaGetLastError());
         return DM_OK;
     }
@@ -305,7 +305,7 @@ extern "C" int dm_bwd_fp8_pass2_cp(const void* ds8_ws, const float* psi_ws, cons
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    bwd2_d128_kernel<<<dim3(cp.nq / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
+    bwd2_d128_kernel<<<dim3(sh.B * hcount, cp.nq / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

@@ -62,10 +62,10 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
     const int nblk = p.N / 128;
     const int nq_blk = p.rm.nq / 128;
-    const int li = nq_blk - 1 - (int)blockIdx.x;      // local row block
+    const int li = nq_blk - 1 - (int)blockIdx.y;      // local row block
     const int I = dm::global_block(p.rm, li);       // its place in the sequence
     const int n_tiles = p.causal ? I + 1 : nblk;
     dm::WaitCtx wc{&s.abort_flag, p.status};
@@ -211,7 +211,7 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    delta_kernel<kDebug, kD><<<dim3(p.rm.nq / 128, sh.B * p.hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
+    delta_kernel<kDebug, kD><<<dim3(sh.B * p.hcount, p.rm.nq / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

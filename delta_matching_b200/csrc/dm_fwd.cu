@@ -56,10 +56,10 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     FwdSmem& s = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
     const int nblk = p.N / 128;
     const int nq_blk = p.rm.nq / 128;
-    const int li = nq_blk - 1 - (int)blockIdx.x;  // local row block, heaviest first
+    const int li = nq_blk - 1 - (int)blockIdx.y;  // local row block, heaviest first
     const int I = dm::global_block(p.rm, li);   // its place in the sequence (decides the causal extent)
     const int n_tiles = p.causal ? I + 1 : nblk;
     dm::WaitCtx wc{&s.abort_flag, p.status};
@@ -369,7 +369,7 @@ extern "C" int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, con
             if (dev >= 0 && dev < 64) attr_done[dev] = true;
         }
     }
-    fwd_d128_kernel<<<dim3(cp.nq / 128, sh.B * hcount), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+    fwd_d128_kernel<<<dim3(sh.B * hcount, cp.nq / 128), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

@@ -50,9 +50,9 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.y, p.h0, p.hcount, p.H, p.Hk);
+    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
     const int nblk = p.N / 128;
-    const int I = nblk - 1 - (int)blockIdx.x;
+    const int I = nblk - 1 - (int)blockIdx.y;
     const int n_tiles = p.causal ? I + 1 : nblk;
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
@@ -258,7 +258,7 @@ int launch_fwd_d256(const void* q8, const void* k8, const void* v8, const float*
     Fwd256Params p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
     const int smem = (int)sizeof(Fwd256Smem) + 1024;
     DM_CUDA(cudaFuncSetAttribute(fwd_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    fwd_d256_kernel<<<dim3(sh.N / 128, sh.B * hcount), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+    fwd_d256_kernel<<<dim3(sh.B * hcount, sh.N / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
