@@ -53,6 +53,7 @@ _SIGNATURES = {
     "dm_bwd_dbg_rowsum": (C.c_int, [_P] * 10 + [DmShape, _P, _P, _P, *_ERR]),
     "dm_probe_mma": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
     "dm_device_status": (C.c_int, [C.POINTER(C.c_int32), *_ERR]),
+    "dm_quant_qv_kpartials": (C.c_int, [_P, DmStrides, _P, DmStrides, _P, DmStrides, DmShape] + [_P] * 5 + [_P, *_ERR]),
     "dm_kmean_partials": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_kmean_fold": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_fold_f32": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int64, C.c_int32, _P, _P, *_ERR]),

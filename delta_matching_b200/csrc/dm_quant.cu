@@ -32,12 +32,12 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
 
 // ---- K mean ---------------------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(256) kmean_partial_kernel(const __nv_bfloat16* __restrict__ k, int64_t sb, int64_t sn, int64_t sh,
-                                                            int Hk, int N, float* __restrict__ partials) {
+__device__ __forceinline__ void kmean_partial_block(int xblk, int bh, const __nv_bfloat16* __restrict__ k, int64_t sb, int64_t sn,
+                                                    int64_t sh, int Hk, int N, float* __restrict__ partials) {
     constexpr int TPC = D / 2;            // threads per 64-row chunk (two columns each)
     constexpr int CPB = 256 / TPC;        // chunks per block
-    const int bh = blockIdx.y, b = bh / Hk, h = bh % Hk;
-    const int chunk = blockIdx.x * CPB + threadIdx.x / TPC;
+    const int b = bh / Hk, h = bh % Hk;
+    const int chunk = xblk * CPB + threadIdx.x / TPC;
     const int c2 = threadIdx.x % TPC;
     const __nv_bfloat16* base = k + b * sb + h * sh + (int64_t)chunk * 64 * sn + 2 * c2;
     float s0 = 0.f, s1 = 0.f;
@@ -49,6 +49,11 @@ __global__ void __launch_bounds__(256) kmean_partial_kernel(const __nv_bfloat16*
     }
     float2* out = reinterpret_cast<float2*>(partials + ((int64_t)bh * (N / 64) + chunk) * D) + c2;
     *out = make_float2(s0, s1);
+}
+template <int D>
+__global__ void __launch_bounds__(256) kmean_partial_kernel(const __nv_bfloat16* __restrict__ k, int64_t sb, int64_t sn, int64_t sh,
+                                                            int Hk, int N, float* __restrict__ partials) {
+    kmean_partial_block<D>(blockIdx.x, blockIdx.y, k, sb, sn, sh, Hk, N, partials);
 }
 
 template <int D>
@@ -63,14 +68,14 @@ __global__ void kmean_fold_kernel(const float* __restrict__ partials, int N, flo
 // ---- block quantizer ------------------------------------------------------------------------------------------------
 // MODE 0 = Q, 1 = K, 2 = V, 3 = dO.
 template <int D, int MODE>
-__global__ void __launch_bounds__(256) quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sn, int64_t sh,
-                                                    const __nv_bfloat16* __restrict__ o, int64_t ob, int64_t on, int64_t oh,
-                                                    const float* __restrict__ km, uint8_t* __restrict__ codes,
-                                                    float* __restrict__ scales, float* __restrict__ delta, int heads, int N, float sm) {
+__device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sn, int64_t sh,
+                                            const __nv_bfloat16* __restrict__ o, int64_t ob, int64_t on, int64_t oh,
+                                            const float* __restrict__ km, uint8_t* __restrict__ codes, float* __restrict__ scales,
+                                            float* __restrict__ delta, int heads, int N, float sm) {
     constexpr int BLK = (MODE == 0 || MODE == 3) ? (D == 128 ? 128 : 64) : (D == 128 ? 64 : 32);
     constexpr int E = D / 32;             // elements per lane
     constexpr int RPW = BLK / 8;          // rows per warp
-    const int blk = blockIdx.x, bh = blockIdx.y, b = bh / heads, h = bh % heads;
+    const int b = bh / heads, h = bh % heads;
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     __shared__ float s_amax[8];
 
@@ -157,6 +162,42 @@ __global__ void __launch_bounds__(256) quant_kernel(const __nv_bfloat16* __restr
     }
 }
 
+template <int D, int MODE>
+__global__ void __launch_bounds__(256) quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sn, int64_t sh,
+                                                    const __nv_bfloat16* __restrict__ o, int64_t ob, int64_t on, int64_t oh,
+                                                    const float* __restrict__ km, uint8_t* __restrict__ codes,
+                                                    float* __restrict__ scales, float* __restrict__ delta, int heads, int N, float sm) {
+    quant_block<D, MODE>(blockIdx.x, blockIdx.y, x, sb, sn, sh, o, ob, on, oh, km, codes, scales, delta, heads, N, sm);
+}
+
+// The three producers of the forward that depend on nothing but the inputs, in one launch: K's per-chunk column sums
+// (first in the grid: the K quantizer waits for them through the fold), the Q quantizer and the V quantizer.  A block
+// does exactly what a block of the separate kernels does, so the results carry the same bits.
+struct PrologueArgs {
+    const __nv_bfloat16 *q, *k, *v;
+    DmStrides qs, ks, vs;
+    uint8_t *q8, *v8;
+    float *q8s, *v8s, *partials;
+    int H, Hk, N;
+    int n_p, pbx, n_q, qbx, vbx;      // blocks of the k-sum part and their count per head; the same for Q; per head for V
+    float sm;
+};
+template <int D>
+__global__ void __launch_bounds__(256) prologue_kernel(const PrologueArgs a) {
+    int i = blockIdx.x;
+    if (i < a.n_p) {
+        kmean_partial_block<D>(i % a.pbx, i / a.pbx, a.k, a.ks.b, a.ks.n, a.ks.h, a.Hk, a.N, a.partials);
+        return;
+    }
+    i -= a.n_p;
+    if (i < a.n_q) {
+        quant_block<D, 0>(i % a.qbx, i / a.qbx, a.q, a.qs.b, a.qs.n, a.qs.h, nullptr, 0, 0, 0, nullptr, a.q8, a.q8s, nullptr, a.H, a.N, a.sm);
+        return;
+    }
+    i -= a.n_q;
+    quant_block<D, 2>(i % a.vbx, i / a.vbx, a.v, a.vs.b, a.vs.n, a.vs.h, nullptr, 0, 0, 0, nullptr, a.v8, a.v8s, nullptr, a.Hk, a.N, a.sm);
+}
+
 // ---- GQA fold -------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) gqa_fold_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int64_t total_vec, int H,
                                                        int Hk, int D) {
@@ -230,6 +271,39 @@ extern "C" int dm_kmean(const void* k, DmStrides ks, int32_t B, int32_t Hk, int3
         kmean_partial_kernel<256><<<dim3(N / 64 / 2, B * Hk), 256, 0, st>>>(kp, ks.b, ks.n, ks.h, Hk, N, partials);
         kmean_fold_kernel<256><<<B * Hk, 256, 0, st>>>(partials, N, km);
     }
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
+extern "C" int dm_quant_qv_kpartials(const void* q, DmStrides qs, const void* k, DmStrides ks, const void* v, DmStrides vs, DmShape s,
+                                     void* q8, float* q8s, void* v8, float* v8s, float* partials, void* stream, char* err, size_t errlen) {
+    int rc = check_geometry(s.B, s.H, s.N, s.D, err, errlen);
+    if (rc) return rc;
+    DM_REQUIRE(s.Hk > 0 && s.H % s.Hk == 0, DM_ERR_ARG, "nheads (%d) must be a positive multiple of nheads_k (%d)", s.H, s.Hk);
+    const void* ptrs[] = {q, k, v, q8, q8s, v8, v8s, partials};
+    const char* names[] = {"q", "k", "v", "q8", "q8s", "v8", "v8s", "partials"};
+    for (int i = 0; i < 8; ++i)
+        if ((rc = dmh::check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
+    if ((rc = check_strides(q, qs, s.D, "q", err, errlen))) return rc;
+    if ((rc = check_strides(k, ks, s.D, "k", err, errlen))) return rc;
+    if ((rc = check_strides(v, vs, s.D, "v", err, errlen))) return rc;
+    DM_REQUIRE(dmh::aligned16(q8) && dmh::aligned16(v8), DM_ERR_ARG, "codes are not 16-byte aligned");
+    const int qblk = s.D == 128 ? 128 : 64, kblk = s.D == 128 ? 64 : 32, cpb = s.D == 128 ? 4 : 2;
+    PrologueArgs a;
+    a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k); a.v = static_cast<const __nv_bfloat16*>(v);
+    a.qs = qs; a.ks = ks; a.vs = vs;
+    a.q8 = static_cast<uint8_t*>(q8); a.v8 = static_cast<uint8_t*>(v8);
+    a.q8s = q8s; a.v8s = v8s; a.partials = partials;
+    a.H = s.H; a.Hk = s.Hk; a.N = s.N;
+    a.pbx = s.N / 64 / cpb; a.n_p = a.pbx * s.B * s.Hk;
+    a.qbx = s.N / qblk; a.n_q = a.qbx * s.B * s.H;
+    a.vbx = s.N / kblk;
+    a.sm = s.D == 128 ? 0.08838834764831845f : 0.0625f;
+    const int64_t total = (int64_t)a.n_p + a.n_q + (int64_t)a.vbx * s.B * s.Hk;
+    DM_REQUIRE(total < ((int64_t)1 << 31), DM_ERR_ARG, "problem too large for one launch");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (s.D == 128) prologue_kernel<128><<<(unsigned)total, 256, 0, st>>>(a);
+    else prologue_kernel<256><<<(unsigned)total, 256, 0, st>>>(a);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }

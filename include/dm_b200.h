@@ -97,6 +97,13 @@ int dm_quant_do(const void* do_bf16, DmStrides dos, const void* o_bf16, DmStride
 int dm_fwd_fp8(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
                DmShape s, int32_t h0, int32_t hcount, void* o_bf16, float* lse, void* stream, char* err, size_t errlen);
 
+/* The producers of the forward that depend only on the inputs, in one launch: K's per-64-row-chunk column sums
+ * (partials [B*Hk, N/64, D], as dm_kmean's scratch), the Q codes / scales and the V codes / scales.  Same bits as dm_quant
+ * (modes 0 and 2) and the first half of dm_kmean; the reference launches these producers one by one
+ * (delta_matching/producers.py:75-94 and :149-204). */
+int dm_quant_qv_kpartials(const void* q, DmStrides qs, const void* k, DmStrides ks, const void* v, DmStrides vs, DmShape s, void* q8,
+                          float* q8s, void* v8, float* v8s, float* partials, void* stream, char* err, size_t errlen);
+
 /* The two halves of dm_kmean for a sequence split across ranks: each rank's per-64-row-chunk sums [B*Hk, N_local/64, D],
  * then (after the exchange, partials in sequence order [B*Hk, N/64, D]) the fold and the division by N.  Same bits as
  * dm_kmean on the whole sequence.  No counterpart in the reference. */

@@ -83,3 +83,19 @@ def test_gqa_fold():
     seq = x.view(2, 256, 2, 4, 128).float()
     acc = ((seq[:, :, :, 0] + seq[:, :, :, 1]) + seq[:, :, :, 2]) + seq[:, :, :, 3]
     assert torch.equal(out, acc.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("D,N", [(128, 512), (256, 256)])
+def test_fused_producers_equal_the_separate_ones(D, N):
+    """The composite forward quantizes Q and V and sums K's chunks in one launch: same codes, scales and K mean as the
+    separate entry points."""
+    from delta_matching_b200 import _lib
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(2, N, 4, D, generator=g).to(torch.bfloat16).cuda()
+    k = (torch.randn(2, N, 2, D, generator=g) + 0.5).to(torch.bfloat16).cuda()
+    v = torch.randn(2, N, 2, D, generator=g).to(torch.bfloat16).cuda()
+    _, _, Q8, Q8s, K8, K8s, V8, V8s = _lib.attn_forward(q, k, v, False)
+    km = _lib.kmean(k)
+    for got, want in zip((Q8, Q8s, K8, K8s, V8, V8s), (*_lib.quant(0, q), *_lib.quant(1, k, km), *_lib.quant(2, v))):
+        assert torch.equal(got.view(torch.uint8) if got.dtype != torch.float32 else got,
+                           want.view(torch.uint8) if want.dtype != torch.float32 else want)
