@@ -194,6 +194,7 @@ def main():
                          "sequence is split across the ranks (delta_matching_b200.cp: zig-zag chunks, K / V codes round an NCCL "
                          "ring, dK / dV partials to the key owners), head_dim 128, reported as strong scaling")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="run the timed steps eagerly instead of replaying a CUDA graph of the step")
     ap.add_argument("--profile", action="store_true", help="only warm-up and timed steps (for ncu captures): no e2e, no per-kernel "
                     "timing, no peak measurement, no CPU baseline")
     args = ap.parse_args()
@@ -268,6 +269,32 @@ def main():
     for _ in range(args.warmup):
         step()
     sync_all()
+    # The step (forward + backward through autograd) is captured once into a CUDA graph and replayed: at the small
+    # configurations the host's launch path (~0.3 ms of Python per step) is as long as the kernels themselves.  Kernels
+    # are counted during the capture.  --no-graph, a sequence split (NCCL inside the step) or a failed capture fall back to
+    # eager steps.
+    graph, launches_per_step = None, None
+    if not args.no_graph and not cp_mode:
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            launches["n"] = 0
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            launches_per_step = launches["n"]
+            for _ in range(2):
+                graph.replay()
+        except Exception as e:                      # noqa: BLE001
+            print(f"bench: CUDA graph capture of the step failed ({type(e).__name__}: {e}); running eager", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    run_step = graph.replay if graph is not None else step
+    sync_all()
     launches["n"] = 0
     times = []
     with ClockSampler(local) as clk:
@@ -278,12 +305,12 @@ def main():
             flush.fill_(1)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            step()
+            run_step()
             e1.record()
             evs.append((e0, e1))
         sync_all()
         times = [a.elapsed_time(b) for a, b in evs]
-    n_launch = launches["n"]
+    n_launch = launches["n"] if graph is None else launches_per_step * args.steps
     total_ms = sum(times)
     if world > 1:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
@@ -298,39 +325,66 @@ def main():
                               "profile_only": True, "gpu_launches": n_launch}), flush=True)
         return
 
-    # ---- end to end with host buffers (H2D of q, k, v, dO; D2H of O, dQ, dK, dV inside the timed region)
-    outs = [torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory(), torch.empty_like(hk).pin_memory(),
-            torch.empty_like(hv).pin_memory()]
+    # ---- end to end with host buffers: every step copies its q, k, v, dO from pinned host memory and its O, dQ, dK, dV back,
+    # all inside the timed region.  The copies dominate (PCIe), so the steps run as a three-stage pipeline on three streams
+    # (copy in, compute, copy out) over two sets of buffers: step i + 1's inputs travel while step i computes and step
+    # i - 1's results leave, which uses both directions of the link at once.
+    hosts = (hq, hk, hv, hdo)
+    nbuf = 2
+    s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dev_in = [[torch.empty(t.shape, dtype=t.dtype, device=dev) for t in hosts] for _ in range(nbuf)]
+    outs = [[torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)] for _ in range(nbuf)]
 
-    def e2e_step():
-        dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
-        dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
-        o = attn(dq_, dk_, dv_)
-        o.backward(ddo)
-        for dst, src in zip(outs, (o.detach(), dq_.grad, dk_.grad, dv_.grad)):
-            dst.copy_(src, non_blocking=True)
+    def e2e_pipeline(n):
+        ev_cmp, ev_out = [None] * nbuf, [None] * nbuf
+        for i in range(n):
+            b = i % nbuf
+            with torch.cuda.stream(s_in):
+                if ev_cmp[b] is not None:
+                    s_in.wait_event(ev_cmp[b])            # step i - nbuf has finished with this set of input buffers
+                for d, h in zip(dev_in[b], hosts):
+                    d.copy_(h, non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in)
+                flush.fill_(1)
+                qq, kk, vv = (t.detach().requires_grad_(True) for t in dev_in[b][:3])
+                o = attn(qq, kk, vv)
+                o.backward(dev_in[b][3])
+                res = (o.detach(), qq.grad, kk.grad, vv.grad)
+                ev_cmp[b] = torch.cuda.Event()
+                ev_cmp[b].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[b])
+                for dst, src in zip(outs[b], res):
+                    dst.copy_(src, non_blocking=True)
+                    src.record_stream(s_out)
+                ev_out[b] = torch.cuda.Event()
+                ev_out[b].record(s_out)
 
-    for _ in range(2):
-        e2e_step()
     sync_all()
-    e2e_times = []
-    for _ in range(max(3, args.steps // 2)):
-        flush.fill_(1)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        e2e_step()
-        e1.record()
-        e1.synchronize()
-        e2e_times.append(e0.elapsed_time(e1))
-    e2e_ms = statistics.mean(e2e_times)
+    e2e_pipeline(3)
+    sync_all()
+    n_e2e = max(4, args.steps // 2)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(s_in)
+    e2e_pipeline(n_e2e)
+    for st_ in (s_in, s_cmp):
+        s_out.wait_stream(st_)
+    e1.record(s_out)
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     nbytes = lambda t: t.numel() * t.element_size()
     e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": sum(nbytes(t) for t in (hq, hk, hv, hdo)), "d2h_bytes_per_step": sum(nbytes(t) for t in outs)}
+           "h2d_bytes_per_step": sum(nbytes(t) for t in hosts), "d2h_bytes_per_step": sum(nbytes(t) for t in outs[0]),
+           "pipeline": "3 streams (copy in / compute / copy out), 2 buffer sets, every step's copies inside the timed region"}
 
+    torch.cuda.empty_cache()      # blocks cached for the pipeline's streams go back before the default stream allocates
     # ---- per-kernel timing (CUDA events around each library call, same inputs, L2 flushed) and the roofline
     roof, kernels = None, {}
     if rank == 0:
@@ -346,7 +400,7 @@ def main():
                 e1.record()
                 acc.setdefault(name, []).append((e0, e1))
                 return r
-            for _ in range(reps):
+            for _ in range(reps + 1):
                 flush.fill_(1)
                 # keep the GPU busy (~2 ms) while the host enqueues the whole chain, so that the events bracket kernel time
                 # only and not the gaps in which the GPU would wait for the host
@@ -369,7 +423,8 @@ def main():
                     timed("pass2", lambda: _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal, cp=cp_map))
                     del dk_, dv_, ws
             torch.cuda.synchronize()
-            kernels = {n: statistics.mean(a.elapsed_time(b) for a, b in ev) for n, ev in acc.items()}
+            # the first repetition also pays for the allocator's first blocks on this stream: leave it out
+            kernels = {n: statistics.median(a.elapsed_time(b) for a, b in ev[1:]) for n, ev in acc.items()}
         u = flops / 7.0                      # one matmul's FLOPs (causal halving already inside `flops`)
         alg = {"fwd": 2 * u, "pass1": 4 * u, "pass2": 1 * u}
         fp8_peak = measure_fp8_peak(dev)
@@ -407,7 +462,8 @@ def main():
                                           ("; the config's KV groups split across ranks" if args.scaling == "strong" else
                                            "; every rank runs the whole config")),
                 "tflops_per_gpu": value / world, "frac_of_nominal_fp8_per_gpu": value / world / NOMINAL_FP8_TFLOPS,
-                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": n_launch, "roofline": roof, "cpu_baseline": cpu}
+                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": n_launch,
+                "step_launch": "CUDA graph replay of one captured step" if graph is not None else "eager", "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
