@@ -2,19 +2,19 @@
 // faithful P basis (per row, per 64-key group) -- csrc/softmax_fq8f.h and csrc/mainloop_fwd_sm90_fp8f.hpp of the
 // reference, restated for tcgen05.
 //
-// One CTA = 128 query rows of one (batch, head).  384 threads: warps 0..7 compute, warps 8..10 are service warps (one
-// issuing lane each, loops converged): warp 8 issues S, warp 9 issues the P V products, warp 10 the TMA loads.  Key tiles
-// of 128 keys (two 64-key groups) are visited from the diagonal tile downwards.  Per tile:
+// One CTA = 128 query rows of one (batch, head).  512 threads in four roles:
+//   warps 0..7   softmax: thread (quarter q, lane, warpgroup g) owns row 32q+lane and key group g of every key tile
+//   warps 8..11  fold: thread = row; they own O (128 fp32 columns per thread) and nothing else
+//   warps 12..14 service (one issuing lane each, loops converged): 12 issues S, 13 issues the P V products, 14 the TMA loads
+// Key tiles of 128 keys (two 64-key groups) are visited from the diagonal tile downwards.  Per tile:
 //   S = Q K^T            4 x tcgen05.mma (M128 N128 K32) into one of two tensor-memory buffers, up to two tiles ahead
-//   softmax              thread (quarter q, lane, warpgroup g) owns row 32q+lane and key group g: group max, running max
-//                        exchanged through shared memory, basis ms_g = max(gm_g*l2, m*l2 - 12) - log2(448),
-//                        codes = e4m3(2^(S*l2 - ms_g)) written to one of two swizzled K-major tiles; the denominator is
-//                        summed from the unrounded p
+//   softmax              group max, running max exchanged through shared memory, basis
+//                        ms_g = max(gm_g*l2, m*l2 - 12) - log2(448), codes = e4m3(2^(S*l2 - ms_g)) written to one of two
+//                        swizzled K-major tiles; the denominator is summed from the unrounded p; the tile's alpha and the
+//                        two weights w_g = v8sc_g * 2^(ms_g - m*l2) per row go to a small ring for the fold warps
 //   D_g = C_g V_g        2 x tcgen05.mma per group into zero-initialised tensor-memory temporaries, issued when the codes
-//                        are in shared memory; they run under the next tile's softmax
-//   O += D_g * w_g       w_g = v8sc_g * 2^(ms_g - m*l2), one tile late; O lives in registers (64 columns per thread) so
-//                        the cross-tile rescale by alpha is a register multiply.  The order of the arithmetic on O is
-//                        that of the straight loop: ... * alpha(t), + D(t) w(t), * alpha(t+1), ...
+//                        are in shared memory and the previous products have been read
+//   O = O * alpha + D_0 w_0 + D_1 w_1   by the fold warps, in that order, while the softmax warps are on the next tile
 // K / V tiles arrive by TMA into a 3-stage ring.  Every mbarrier wait is bounded.
 #include "dm_attn_common.cuh"
 #include "dm_host.h"
@@ -23,8 +23,9 @@ namespace {
 
 constexpr int kTile = 128 * 128;   // bytes of one e4m3 tile (128 rows x 128 bytes)
 constexpr int kStages = 3;
-constexpr int kThreads = 384;
-constexpr int kComputeThreads = 256;
+constexpr int kThreads = 512;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kRing = 4;           // depth of the per-tile row-constant ring between softmax and fold warps
 
 struct FwdSmem {
     alignas(1024) uint8_t q[kTile];
@@ -32,9 +33,11 @@ struct FwdSmem {
     alignas(1024) uint8_t v[kStages][kTile];
     alignas(1024) uint8_t p[2][kTile];
     float gmax[2][2][128];            // [tile parity][key group][row]
-    float wgt[2][2][128];
+    float wgt[kRing][2][128];         // [tile % kRing][key group][row]
+    float alpha[kRing][128];
     float lsum[2][128];
-    uint64_t bar_q, bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2], bar_d_full;
+    uint64_t bar_q, bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2], bar_d_full[2], bar_d_free,
+        bar_l;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -75,8 +78,10 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             dm::mbar_init(&s.bar_s_full[i], 1);
             dm::mbar_init(&s.bar_s_free[i], 8);
             dm::mbar_init(&s.bar_codes[i], 8);
+            dm::mbar_init(&s.bar_d_full[i], 1);
         }
-        dm::mbar_init(&s.bar_d_full, 1);
+        dm::mbar_init(&s.bar_d_free, 4);
+        dm::mbar_init(&s.bar_l, 8);
         dm::fence_mbar_init();
         dm::tma_prefetch_desc(&tm_q);
         dm::tma_prefetch_desc(&tm_k);
@@ -88,22 +93,28 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     dm::tc_fence_after();
     const uint32_t tmem = s.tmem_base;
     const uint32_t t_d0 = tmem + 256, t_d1 = tmem + 384;      // S buffers at columns [0, 128) and [128, 256)
+    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
 
-    if (warp >= 8) {
+    if (warp >= 12) {
         // =============================================================== service warps
         dm::reg_dec<40>();
         const bool leader = lane == 0;
         const int kv_row0 = hc.bhk * p.N;
         constexpr uint32_t kSub = kTile >> 4;
-        if (warp == 8) {
-            // ---- S = Q K^T of tile `it` into buffer it & 1
+        if (warp == 12) {
+            // ---- S = Q K^T of tile `it` into buffer it & 1.  The code tile of the same parity is rewritten by the softmax
+            // of this tile, so the products of tile it - 2, which read it, must be complete: waiting for them here gates
+            // the softmax warps through S.
             constexpr uint32_t idesc_s = dm::idesc_e4m3(128, 128, false, false);
             const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q)), k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0]));
             dm::mbar_wait(&s.bar_q, 0, wc);
             for (int it = 0; it < n_tiles; ++it) {
                 const int st = it % kStages, b = it & 1;
                 dm::mbar_wait(&s.bar_kv[st], (it / kStages) & 1, wc);
-                if (it >= 2) dm::mbar_wait(&s.bar_s_free[b], ((it - 2) >> 1) & 1, wc);
+                if (it >= 2) {
+                    dm::mbar_wait(&s.bar_s_free[b], ((it - 2) >> 1) & 1, wc);
+                    dm::mbar_wait(&s.bar_d_full[b], ((it - 2) >> 1) & 1, wc);
+                }
                 dm::tc_fence_after();
                 const uint32_t ks = k_lo + st * kSub, ts = tmem + b * 128;
                 if (leader) {
@@ -114,29 +125,30 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 }
                 __syncwarp();
             }
-        } else if (warp == 9) {
-            // ---- D_g = C_g V_g for both key groups once the codes of tile `it` are in shared memory and the products of
-            // tile it - 1 have been folded (the compute warps arrive on bar_codes after both)
+        } else if (warp == 13) {
+            // ---- D_g = C_g V_g for both key groups once the codes of tile `it` are in shared memory and the fold warps
+            // have read the products of tile it - 1
             constexpr uint32_t idesc_pv = dm::idesc_e4m3(128, 128, false, true);
             const uint32_t p_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.p[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
             for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % kStages;
+                const int st = it % kStages, b = it & 1;
                 dm::mbar_wait(&s.bar_kv[st], (it / kStages) & 1, wc);
-                dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
+                dm::mbar_wait(&s.bar_codes[b], (it >> 1) & 1, wc);
+                if (it >= 1) dm::mbar_wait(&s.bar_d_free, (it - 1) & 1, wc);
                 dm::tc_fence_after();
-                const uint32_t pa = p_lo + (it & 1) * kSub, va = v_lo + st * kSub;
+                const uint32_t pa = p_lo + b * kSub, va = v_lo + st * kSub;
                 if (leader) {
                     // group gg: codes columns [64 gg, 64 gg + 64) (K-major, +4 per 64 bytes), V rows [64 gg, +64) (MN-major, +512)
                     dm::umma_e4m3_lo<false>(t_d0, pa, va, idesc_pv);
                     dm::umma_e4m3_lo<true>(t_d0, pa + 2, va + 256, idesc_pv);
                     dm::umma_e4m3_lo<false>(t_d1, pa + 4, va + 512, idesc_pv);
                     dm::umma_e4m3_lo<true>(t_d1, pa + 6, va + 768, idesc_pv);
-                    dm::umma_commit(&s.bar_d_full);
+                    dm::umma_commit(&s.bar_d_full[b]);
                     dm::umma_commit(&s.bar_kv_free[st]);       // K was read by S long ago, V just now
                 }
                 __syncwarp();
             }
-        } else if (warp == 10) {
+        } else if (warp == 14) {
             // ---- TMA loads: Q once, K / V tiles as far ahead as the ring allows
             const int q_row0 = hc.bh * p.rm.nq + li * 128;
             if (leader) {
@@ -154,43 +166,70 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 __syncwarp();
             }
         }
+    } else if (warp >= 8) {
+        // =============================================================== fold warps: thread = row, all 128 columns of O
+        dm::reg_inc<208>();
+        const int row = (warp & 3) * 32 + lane;
+        float o_acc[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) o_acc[i] = 0.f;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int b = it & 1, r = it % kRing;
+            dm::mbar_wait(&s.bar_d_full[b], (it >> 1) & 1, wc);      // also orders the ring slot written before the codes
+            dm::tc_fence_after();
+            const float alpha = s.alpha[r][row], w0 = s.wgt[r][0][row], w1 = s.wgt[r][1][row];
+            uint32_t sa[32], sb[32];
+            dm::tmem_ld32(dm::tmem_addr(t_d0, lane_base, 0), sa);
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < 128; i += 2) dm::mul2(o_acc[i], o_acc[i + 1], o_acc[i], o_acc[i + 1], alpha, alpha);
+            }
+            // eight 32-column pieces (group 0 columns 0..127, then group 1), the next one in flight while one is added
+#pragma unroll
+            for (int pc = 0; pc < 8; ++pc) {
+                uint32_t* cur = (pc & 1) ? sb : sa;
+                uint32_t* nxt = (pc & 1) ? sa : sb;
+                dm::tmem_ld_wait();
+                if (pc < 7) dm::tmem_ld32(dm::tmem_addr((pc + 1 < 4) ? t_d0 : t_d1, lane_base, 32 * ((pc + 1) & 3)), nxt);
+                const float w = (pc < 4) ? w0 : w1;
+                const int c0 = 32 * (pc & 3);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                    dm::fma2(o_acc[c0 + i], o_acc[c0 + i + 1], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]), w, o_acc[c0 + i],
+                             o_acc[c0 + i + 1]);
+            }
+            dm::tc_fence_before();
+            dm::mbar_arrive_warp(&s.bar_d_free);
+        }
+        // ---- epilogue: the softmax warps have left both halves of the denominator
+        dm::mbar_wait(&s.bar_l, 0, wc);
+        const float l = s.lsum[0][row] + s.lsum[1][row];
+        const bool dead = (l == 0.f) || (l != l);
+        const float inv = dead ? 0.f : 1.0f / l;
+        const int n_glob = li * 128 + row;          // row inside the (local) Q-side tensors
+        __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
+                w4[e] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
     } else {
-        // =============================================================== compute warps
-        dm::reg_inc<232>();
-        const int g = warp >> 2;                  // warpgroup = key group inside the tile, and the 64-column half of O
+        // =============================================================== softmax warps
+        const int g = warp >> 2;                  // warpgroup = key group inside the tile
         const int row = (warp & 3) * 32 + lane;   // query row inside the block = tensor-memory lane
-        const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
         const float q8sc = p.q8s[(int64_t)hc.bh * nq_blk + li];
         const float* ksp = p.k8s + (int64_t)hc.bhk * (p.N / 64) + g;
         const float* vsp = p.v8s + (int64_t)hc.bhk * (p.N / 64) + g;
         float m_run = -INFINITY, l_part = 0.f;
-        float o_acc[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) o_acc[i] = 0.f;
-
-        // the products of tile `t` into O: both groups' 64 columns of this thread, 16 at a time
-        auto fold = [&](int t) {
-            dm::mbar_wait(&s.bar_d_full, t & 1, wc);
-            dm::tc_fence_after();
-#pragma unroll
-            for (int gg = 0; gg < 2; ++gg) {
-                const float w = s.wgt[t & 1][gg][row];
-                const uint32_t td = gg ? t_d1 : t_d0;
-                uint32_t stage[32];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    dm::tmem_ld32(dm::tmem_addr(td, lane_base, g * 64 + 32 * h), stage);
-                    dm::tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[32 * h + i] = fmaf(__uint_as_float(stage[i]), w, o_acc[32 * h + i]);
-                }
-            }
-            dm::tc_fence_before();
-        };
 
         float ks_n = ksp[2 * (n_tiles - 1)], vs_n = vsp[2 * (n_tiles - 1)];
         for (int it = 0; it < n_tiles; ++it) {
-            const int j = n_tiles - 1 - it, b = it & 1;
+            const int j = n_tiles - 1 - it, b = it & 1, r = it % kRing;
             const float ks = ks_n, vs = vs_n;
             if (it + 1 < n_tiles) {
                 ks_n = ksp[2 * (j - 1)];
@@ -218,71 +257,57 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             } else {
                 float gm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    sv[c] *= dsc;
+                for (int c = 0; c < 64; c += 2) {
+                    dm::mul2(sv[c], sv[c + 1], sv[c], sv[c + 1], dsc, dsc);
                     gm4[c & 3] = fmaxf(gm4[c & 3], sv[c]);
+                    gm4[(c + 1) & 3] = fmaxf(gm4[(c + 1) & 3], sv[c + 1]);
                 }
                 gm = fmaxf(fmaxf(gm4[0], gm4[1]), fmaxf(gm4[2], gm4[3]));
             }
             s.gmax[b][g][row] = gm;
-            dm::named_bar_sync(1, kComputeThreads);
+            dm::named_bar_sync(1, kSoftmaxThreads);
             const float tile_max = fmaxf(s.gmax[b][0][row], s.gmax[b][1][row]);
             const float m_new = fmaxf(m_run, tile_max);
             const float m_cur = (m_new == -INFINITY) ? 0.f : m_new;
             const float alpha = dm::ex2((m_run - m_cur) * dm::kLog2e);
             const float ml2 = m_cur * dm::kLog2e;
             const float ms = fmaxf(gm * dm::kLog2e, ml2 - dm::kPhatFloorB) - dm::kLog2_448;
+            const float sigma = dm::ex2(ms - ml2);
+            // the ring slot of tile it - kRing has been read: its fold came before the fold of tile it - 3, whose release
+            // of the product buffers came before the products of tile it - 2, which S of this tile waited for
+            s.wgt[r][g][row] = vs * sigma;
+            if (g == 0) s.alpha[r][row] = alpha;
             float part = 0.f;
             uint32_t codes[16];
+            const float nms = -ms;
 #pragma unroll
             for (int c = 0; c < 64; c += 4) {
-                const float p0 = dm::ex2(fmaf(sv[c], dm::kLog2e, -ms));
-                const float p1 = dm::ex2(fmaf(sv[c + 1], dm::kLog2e, -ms));
-                const float p2 = dm::ex2(fmaf(sv[c + 2], dm::kLog2e, -ms));
-                const float p3 = dm::ex2(fmaf(sv[c + 3], dm::kLog2e, -ms));
+                float x0, x1, x2, x3;
+                dm::fma2(x0, x1, sv[c], sv[c + 1], dm::kLog2e, nms, nms);
+                dm::fma2(x2, x3, sv[c + 2], sv[c + 3], dm::kLog2e, nms, nms);
+                const float p0 = dm::ex2(x0), p1 = dm::ex2(x1), p2 = dm::ex2(x2), p3 = dm::ex2(x3);
                 part += (p0 + p1) + (p2 + p3);
                 codes[c >> 2] = dm::cvt_e4m3x4(p0, p1, p2, p3);
             }
-            const float sigma = dm::ex2(ms - ml2);
             l_part = fmaf(l_part, alpha, sigma * part);
-            s.wgt[b][g][row] = vs * sigma;
-            // the tile of parity b was last read by the products of tile it - 2, folded one iteration ago
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 *reinterpret_cast<uint4*>(s.p[b] + dm::sw128(row, g * 64 + c * 16)) =
                     make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
-            dm::fence_proxy_async_smem();
-            // ---- the previous tile's products, complete by now, then this tile's rescale
-            if (it > 0) fold(it - 1);
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) o_acc[i] *= alpha;
-            }
             m_run = m_new;
+            dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[b]);
         }
-        dm::named_bar_sync(1, kComputeThreads);          // the other warpgroup's weight of the last tile
-        fold(n_tiles - 1);
 
-        // ---- epilogue
+        // ---- epilogue: denominator halves to the fold warps, LSE
         s.lsum[g][row] = l_part;
-        dm::named_bar_sync(1, kComputeThreads);
-        const float l = s.lsum[0][row] + s.lsum[1][row];
-        const bool dead = (l == 0.f) || (l != l);
-        const float inv = dead ? 0.f : 1.0f / l;
-        const int n_glob = li * 128 + row;          // row inside the (local) Q-side tensors
-        __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128 + g * 64;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint32_t w4[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 t = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
-                w4[e] = *reinterpret_cast<uint32_t*>(&t);
-            }
-            reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        dm::mbar_arrive_warp(&s.bar_l);
+        dm::named_bar_sync(1, kSoftmaxThreads);
+        if (g == 0) {
+            const float l = s.lsum[0][row] + s.lsum[1][row];
+            const bool dead = (l == 0.f) || (l != l);
+            p.lse[(int64_t)hc.bh * p.rm.nq + li * 128 + row] = dead ? -INFINITY : m_run + logf(l);
         }
-        if (g == 0) p.lse[(int64_t)hc.bh * p.rm.nq + n_glob] = dead ? -INFINITY : m_run + logf(l);
     }
     dm::tc_fence_before();
     __syncthreads();
