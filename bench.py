@@ -274,7 +274,7 @@ def main():
     # are counted during the capture.  --no-graph, a sequence split (NCCL inside the step) or a failed capture fall back to
     # eager steps.
     graph, launches_per_step = None, None
-    if not args.no_graph and not cp_mode:
+    if not args.no_graph and not cp_mode and not args.profile:
         try:
             side = torch.cuda.Stream(dev)
             side.wait_stream(torch.cuda.current_stream())
