@@ -1,11 +1,12 @@
 // Pass 1 of the backward, head_dim 128: dK and dV per query head, plus the e4m3 dS' code tiles and their psi scales for
 // pass 2 (csrc/mainloop_bwd_sm90_fp8r.hpp:695-952 of the reference, restated for tcgen05).
 //
-// One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  384 threads:
-// warps 0..7 compute (232 registers each after setmaxnreg); warps 8..11, one per scheduler, each run one service loop so
-// that no instruction issue sits on the compute warps' path and no service waits behind another: warp 8 issues the S^T /
-// dP^T tcgen05.mma, warp 9 the dK / dV tcgen05.mma and the dS' TMA store, warp 10 the TMA loads, warp 11 produces the
-// per-row constants.  The sides meet only through mbarriers.
+// One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  512 threads
+// in three roles that meet only through mbarriers:
+//   warps 0..7   softmax: P-hat, dS', the tile amax, psi and the two code tiles of every m-block; they hold no accumulator
+//   warps 8..11  fold: thread = key; they own dK (128 fp32 columns in registers) and drive dV's accumulator in tensor memory
+//   warps 12..15 service, one per scheduler, loops converged with one issuing lane: 12 issues the S^T / dP^T tcgen05.mma,
+//                13 the dK / dV tcgen05.mma and the dS' TMA store, 14 the TMA loads, 15 produces the per-row constants
 // Everything is computed transposed (keys x rows): tensor-memory lane = key, so the per-key scales are per-thread
 // constants.  Per m-block:
 //   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each into one of two (S | dP) tensor-memory buffers, issued
@@ -16,8 +17,9 @@
 //                                  the finished 128 x 128 dS' tile of a row pair leaves by one TMA store
 //   dV_tmp (+)= P-hat8^T dO8       M128 N128 K32 x 2, zero-initialised on the first m-block of a 128-row dO scale block
 //   dK_tmp  = dS'8^T Q8            M128 N128 K32 x 2, zero-initialised
-//   dK += dK_tmp * (psi 2^-8 q8sc)  and, once per 128-row block,  dV += dV_tmp * (2^-8 do8sc)   in registers, one m-block
-//                                  late, so the products complete under the next m-block's arithmetic
+//   dK += dK_tmp * (psi 2^-8 q8sc)   by the fold warps, in registers, while the softmax warps are on the next m-block
+//   dV += dV_tmp * (2^-8 do8sc)       once per 128-row dO scale block: dV's fp32 accumulator lives in tensor memory
+//                                  (columns [384, 512)); the fold warps read product and accumulator, add, and store it back
 // Q8 / dO8 m-block tiles serve twice: K-major as the B operand of S^T / dP^T and MN-major as the B operand of dK / dV.
 // The dS' tile layout in global memory is [key][row] (128 x 128 bytes), which pass 2 reads as an MN-major A operand.
 #include "dm_attn_common.cuh"
@@ -31,8 +33,9 @@ namespace {
 
 constexpr int kTile = 128 * 128;
 constexpr int kHalf = 64 * 128;
-constexpr int kComputeThreads = 256;
-constexpr int kThreads = 384;          // two compute warpgroups + one issuer warpgroup (only its first warp works)
+constexpr int kComputeThreads = 256;   // the softmax warps
+constexpr int kThreads = 512;          // two softmax warpgroups, one fold warpgroup, one service warpgroup
+constexpr int kRing = 4;               // depth of the per-m-block scale ring between softmax and fold warps
 
 // Geometry per head dim.  head_dim 256 (csrc/mainloop_bwd_sm90_fp8v10.hpp:1674-1761 of the reference): a code row is two
 // 128-byte sub-tiles, K / V scales per 32 keys, Q / dO scales per 64-row m-block, psi per 64 rows x 64 keys (so a CTA's 128
@@ -59,8 +62,9 @@ struct Bwd1Smem {
     alignas(16) float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
     alignas(16) float dlk[3][kGrp][64];               // -delta * k8s(group) per row
     float sc[3][2];                                   // q8sc, do8sc of the m-block (same ring)
+    float gf[kRing][4];                               // per m-block: dK scale of key half 0, of key half 1, dV scale
     float amax[2][8];
-    uint64_t bar_kv, bar_qdo[kStages], bar_stage_free[kStages], bar_sp_full[2], bar_sp_free[2], bar_codes[2], bar_dkv_full,
+    uint64_t bar_kv, bar_qdo[kStages], bar_stage_free[kStages], bar_sp_full, bar_sp_free, bar_codes[2], bar_dkv_full[2],
         bar_dkv_free, bar_ds_free[2], bar_rows_full[3], bar_rows_free[3];
     uint32_t tmem_base;
     int abort_flag;
@@ -124,49 +128,56 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::mbar_init(&s.bar_rows_free[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            dm::mbar_init(&s.bar_sp_full[i], 1);
-            dm::mbar_init(&s.bar_sp_free[i], 8);
             dm::mbar_init(&s.bar_codes[i], 8);
             dm::mbar_init(&s.bar_ds_free[i], 1);
+            dm::mbar_init(&s.bar_dkv_full[i], 1);
         }
-        dm::mbar_init(&s.bar_dkv_full, 1);
-        dm::mbar_init(&s.bar_dkv_free, 8);
+        dm::mbar_init(&s.bar_sp_full, 1);
+        dm::mbar_init(&s.bar_sp_free, 8);
+        dm::mbar_init(&s.bar_dkv_free, 4);
         dm::fence_mbar_init();
     }
     if (warp == 0) dm::tmem_alloc(&s.tmem_base, 512);
     dm::tc_fence_before();
     __syncthreads();
     dm::tc_fence_after();
+    // tensor memory: S^T | dP^T at columns [0, 64) | [64, 128), dV product [128, 256), dK product [256, 384), dV accumulator
+    // [384, 512)
     const uint32_t tmem = s.tmem_base;
-    const uint32_t t_dv = tmem + 256, t_dk = tmem + 384;
+    const uint32_t t_dv = tmem + 128, t_dk = tmem + 256, t_dva = tmem + 384;
+    const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
+    const int key = (warp & 3) * 32 + lane;       // tensor-memory lane of the softmax and fold threads
+    const int khalf = key >> 6;                   // 64-key half (the psi tile at head_dim 256)
 
-    if (warp >= 8) {
-        // =============================================================== service warps 8..11, one per scheduler
+    if (warp >= 12) {
+        // =============================================================== service warps 12..15, one per scheduler
         // Each runs its loop converged (all lanes wait and compute the same addresses, so they stay in uniform registers)
         // and lane 0 alone executes the asynchronous instruction.
         dm::reg_dec<40>();
         const bool leader = lane == 0;
         const int kv_row0 = hc.bhk * p.N + J * 128;
-        if (warp == 8) {
-            // ---- S^T = K Q^T and dP^T = V dO^T of m-block `it` into product buffer it & 1, up to two m-blocks ahead
+        if (warp == 12) {
+            // ---- S^T = K Q^T and dP^T = V dO^T of m-block `it`, as soon as the softmax warps have read the previous pair
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;   // descriptor strides
             const uint32_t k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
             const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
             if (n_it > 0) dm::mbar_wait(&s.bar_kv, 0, wc);
             for (int it = 0; it < n_it; ++it) {
-                const int st = it % kStages, b = it & 1;
-                if (it >= 2) dm::mbar_wait(&s.bar_sp_free[b], ((it - 2) >> 1) & 1, wc);
+                const int st = it % kStages;
                 dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
-                // the compute warps read the row constants of this m-block once its products are there: waiting here saves
+                // the softmax warps read the row constants of this m-block once its products are there: waiting here saves
                 // them a wait of their own
                 dm::mbar_wait(&s.bar_rows_full[it % 3], (it / 3) & 1, wc);
-                // The compute warps write the dS' codes of this m-block into the tile of its row pair; the TMA store that
-                // drains the pair two back must have read that tile.  Gating the products gates the compute warps.
+                if (it >= 1) dm::mbar_wait(&s.bar_sp_free, (it - 1) & 1, wc);
+                // The softmax warps rewrite, in this m-block, the P-hat half tile that the dV product of m-block it - 2 read,
+                // and (first m-block of a row pair) the dS' tile that the TMA store of the pair two back drains: both must
+                // be done.  Gating the products gates the softmax warps.
+                if (it >= 2) dm::mbar_wait(&s.bar_dkv_full[it & 1], ((it - 2) >> 1) & 1, wc);
                 const int pair = it >> 1;           // m_lo is even: pairs start at it = 0
                 if (zh == 0 && (it & 1) == 0 && pair >= 2) dm::mbar_wait(&s.bar_ds_free[pair & 1], ((pair - 2) >> 1) & 1, wc);
                 dm::tc_fence_after();
-                const uint32_t t_s = tmem + b * 128, t_dp = t_s + 64;
+                const uint32_t t_s = tmem, t_dp = tmem + 64;
                 const uint32_t qs = q_lo + st * kStageQ, dos = do_lo + st * kStageQ;
                 if (leader) {
 #pragma unroll
@@ -185,13 +196,13 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                             else dm::umma_e4m3_lo<true>(t_dp, v_lo + hh * kSub + 2 * k, dos + hh * kSubQ + 2 * k, idesc_sp);
                         }
                     }
-                    dm::umma_commit(&s.bar_sp_full[b]);
+                    dm::umma_commit(&s.bar_sp_full);
                 }
                 __syncwarp();
             }
-        } else if (warp == 9) {
-            // ---- dV_tmp (+)= P-hat8^T dO8 and dK_tmp = dS'8^T Q8 once the codes of m-block `it` are in shared memory; the
-            // finished dS' tile of a row pair leaves by one TMA store
+        } else if (warp == 13) {
+            // ---- dV_tmp (+)= P-hat8^T dO8 and dK_tmp = dS'8^T Q8 once the codes of m-block `it` are in shared memory and
+            // the fold warps have read the previous products; the finished dS' tile of a row pair leaves by one TMA store
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
             constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;
             const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
@@ -200,7 +211,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             for (int it = 0; it < n_it; ++it) {
                 const int st = it % kStages, par = it & 1, pp = (it >> 1) & 1;
                 dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
-                // every compute warp is past the row constants of this m-block: their ring slot may be refilled
+                // every softmax warp is past the row constants of this m-block: their ring slot may be refilled
                 if (leader) dm::mbar_arrive(&s.bar_rows_free[it % 3]);
                 if (it >= 1) dm::mbar_wait(&s.bar_dkv_free, (it - 1) & 1, wc);
                 dm::tc_fence_after();
@@ -212,7 +223,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                     dm::umma_e4m3_lo<true>(t_dv, pa + 2, dos + 256, idesc_dkv);
                     dm::umma_e4m3_lo<false>(t_dk, da, qs, idesc_dkv);
                     dm::umma_e4m3_lo<true>(t_dk, da + 2, qs + 256, idesc_dkv);
-                    dm::umma_commit(&s.bar_dkv_full);
+                    dm::umma_commit(&s.bar_dkv_full[it & 1]);
                     dm::umma_commit(&s.bar_stage_free[st]);      // the Q / dO stage has been read for the last time
                     if (par == 1 && zh == 0) {
                         dm::tma_store_2d(&tm_ds, 0, ds_row0 + (it >> 1) * (nbn * 128), s.ds[pp]);
@@ -228,7 +239,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
                 if (leader) dm::tma_store_wait_all0();
             }
-        } else if (warp == 10) {
+        } else if (warp == 14) {
             // ---- TMA loads: K / V once, then the Q8 / dO8 tiles of the m-blocks as far ahead as the ring allows
             const int q_row0 = hc.bh * p.rm.nq + m_lo * 64;
             if (n_it > 0 && leader) {
@@ -252,7 +263,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 __syncwarp();
             }
         } else {
-            // ---- per-row constants of the m-blocks, three ahead: 8 - lse * log2e and delta * k8s(group) for the 64 rows
+            // ---- per-row constants of the m-blocks, three ahead: 8 - lse * log2e and -delta * k8s(group) for the 64 rows
             // (two per lane), and the Q / dO scales of the m-block
             const int nsq = kD == 128 ? nq_blk : nbm;
             float kk[kGrp];
@@ -275,48 +286,122 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 if (leader) dm::mbar_arrive(&s.bar_rows_full[slot]);
             }
         }
-    } else {
-        // =============================================================== compute warps
+    } else if (warp >= 8) {
+        // =============================================================== fold warps: thread = key, all 128 columns
         dm::reg_inc<232>();
-        const int g = warp >> 2;                      // column half: rows [32 g, 32 g + 32) of S^T, d [64 g, 64 g + 64) of dK / dV
-        const int key = (warp & 3) * 32 + lane;       // tensor-memory lane
+        const int kgrp = key / kKPS;
+        float dk_acc[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) dk_acc[i] = 0.f;
+        bool dv_started = false;                  // the tensor-memory accumulator holds something
+        for (int it = 0; it < n_it; ++it) {
+            const int r = it % kRing;
+            dm::mbar_wait(&s.bar_dkv_full[it & 1], (it >> 1) & 1, wc);   // also orders the ring slot written before the codes
+            dm::tc_fence_after();
+            const float gk = s.gf[r][kD == 128 ? 0 : khalf], fv = s.gf[r][2];
+            uint32_t sa[32], sb[32];
+            // dK: four 32-column pieces, the next one in flight while one is added
+#define DM_DK_PIECE(PC, CUR, NXT)                                                                                       \
+            dm::tmem_ld_wait();                                                                                         \
+            if ((PC) < 3) dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, 32 * ((PC) + 1)), NXT);                           \
+            _Pragma("unroll") for (int i = 0; i < 32; i += 2)                                                            \
+                dm::fma2(dk_acc[32 * (PC) + i], dk_acc[32 * (PC) + i + 1], __uint_as_float(CUR[i]), __uint_as_float(CUR[i + 1]), gk, \
+                         dk_acc[32 * (PC) + i], dk_acc[32 * (PC) + i + 1]);
+            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, 0), sa);
+            DM_DK_PIECE(0, sa, sb)
+            DM_DK_PIECE(1, sb, sa)
+            DM_DK_PIECE(2, sa, sb)
+            DM_DK_PIECE(3, sb, sa)
+#undef DM_DK_PIECE
+            // dV: the product of a whole dO scale block (two m-blocks at head_dim 128, one at 256) into the accumulator
+            if (kD == 256 || (it & 1) == 1) {
+#pragma unroll
+                for (int pc = 0; pc < 4; ++pc) {
+                    dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, 32 * pc), sa);
+                    if (dv_started) dm::tmem_ld32(dm::tmem_addr(t_dva, lane_base, 32 * pc), sb);
+                    dm::tmem_ld_wait();
+                    if (dv_started) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float y0, y1;
+                            dm::fma2(y0, y1, __uint_as_float(sa[i]), __uint_as_float(sa[i + 1]), fv, __uint_as_float(sb[i]),
+                                     __uint_as_float(sb[i + 1]));
+                            sa[i] = __float_as_uint(y0);
+                            sa[i + 1] = __float_as_uint(y1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float y0, y1;
+                            dm::fma2(y0, y1, __uint_as_float(sa[i]), __uint_as_float(sa[i + 1]), fv, 0.f, 0.f);
+                            sa[i] = __float_as_uint(y0);
+                            sa[i + 1] = __float_as_uint(y1);
+                        }
+                    }
+                    dm::tmem_st32(dm::tmem_addr(t_dva, lane_base, 32 * pc), sa);
+                }
+                dm::tmem_st_wait();
+                dv_started = true;
+            }
+            dm::tc_fence_before();
+            dm::mbar_arrive_warp(&s.bar_dkv_free);
+        }
+
+        // ---- epilogue: dK *= 1 / k8s, dV from its accumulator; one row of 128 columns per thread, per query head
+        const float ik = 1.0f / p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
+        const int n_glob = J * 128 + key;
+        const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128;
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+            float dvv[32];
+            if (dv_started) {
+                dm::tmem_ld32(dm::tmem_addr(t_dva, lane_base, 32 * pc), reinterpret_cast<uint32_t*>(dvv));
+                dm::tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dvv[i] = 0.f;
+            }
+            if (p.out_fp32) {
+                float4* ok = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dk) + off + 32 * pc);
+                float4* ov = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dv) + off + 32 * pc);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    ok[c] = make_float4(dk_acc[32 * pc + 4 * c] * ik, dk_acc[32 * pc + 4 * c + 1] * ik, dk_acc[32 * pc + 4 * c + 2] * ik,
+                                        dk_acc[32 * pc + 4 * c + 3] * ik);
+                    ov[c] = make_float4(dvv[4 * c], dvv[4 * c + 1], dvv[4 * c + 2], dvv[4 * c + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t wk[4], wv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 32 * pc + 8 * c + 2 * e;
+                        __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[i] * ik, dk_acc[i + 1] * ik);
+                        __nv_bfloat162 b = __floats2bfloat162_rn(dvv[8 * c + 2 * e], dvv[8 * c + 2 * e + 1]);
+                        wk[e] = *reinterpret_cast<uint32_t*>(&a);
+                        wv[e] = *reinterpret_cast<uint32_t*>(&b);
+                    }
+                    reinterpret_cast<uint4*>(p.dk + off + 32 * pc)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+                    reinterpret_cast<uint4*>(p.dv + off + 32 * pc)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
+        }
+        dm::tc_fence_before();
+    } else {
+        // =============================================================== softmax warps
+        dm::reg_dec<112>();
+        const int g = warp >> 2;                      // row half: rows [32 g, 32 g + 32) of the m-block
         const int kgrp = key / kKPS;                  // K / V scale group inside the block
-        const int khalf = key >> 6;                   // 64-key half (the psi tile at head_dim 256)
-        const uint32_t lane_base = (uint32_t)(warp & 3) * 32;
         const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         // the local 128-row block on the diagonal of this key block (none: -1); it is the first one of the causal loop
         const int diag_lb = (p.causal && n_it > 0 && dm::global_block(p.rm, m_lo >> 1) == J) ? (m_lo >> 1) : -1;
         float g_max = 0.f;
-        float dk_acc[64], dv_acc[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) { dk_acc[i] = 0.f; dv_acc[i] = 0.f; }
-
-        float g_prev = 0.f, f_prev = 0.f;
-
-        auto fold = [&](int it, float g_fold, float f_fold) {
-            dm::mbar_wait(&s.bar_dkv_full, it & 1, wc);
-            dm::tc_fence_after();
-            float t[64];
-            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
-            dm::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 64; ++i) dk_acc[i] = fmaf(t[i], g_fold, dk_acc[i]);
-            if (kD == 256 || ((m_lo + it) & 1) == 1) {
-                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64), reinterpret_cast<uint32_t*>(t));
-                dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t) + 32);
-                dm::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 64; ++i) dv_acc[i] = fmaf(t[i], f_fold, dv_acc[i]);
-            }
-            dm::tc_fence_before();
-            dm::mbar_arrive_warp(&s.bar_dkv_free);
-        };
 
         for (int it = 0; it < n_it; ++it) {
             const int mb = m_lo + it, par = mb & 1, sb = it & 1, rb = it % 3;
-            dm::mbar_wait(&s.bar_sp_full[sb], (it >> 1) & 1, wc);
+            dm::mbar_wait(&s.bar_sp_full, it & 1, wc);
             dm::tc_fence_after();
             // the ring slot of this m-block's row constants and scales was complete before S^T / dP^T were issued
             const float q8sc = s.sc[rb][0], do8sc = s.sc[rb][1];
@@ -326,9 +411,9 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory.  S^T first: the exponentials run while
             // dP^T is still on its way from tensor memory.
             float sv[32], ds[32];
-            dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
+            dm::tmem_ld32(dm::tmem_addr(tmem, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
             dm::tmem_ld_wait();
-            dm::tmem_ld32(dm::tmem_addr(tmem + sb * 128 + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
+            dm::tmem_ld32(dm::tmem_addr(tmem + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
             const bool diag = (mb >> 1) == diag_lb;
             const int row_in_pair = par * 64 + g * 32;     // row offset of column 0 inside the 128-row pair
             const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 32]);
@@ -349,7 +434,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
             dm::tmem_ld_wait();
             dm::tc_fence_before();
-            dm::mbar_arrive_warp(&s.bar_sp_free[sb]);      // this (S | dP) buffer may be overwritten
+            dm::mbar_arrive_warp(&s.bar_sp_free);          // the (S | dP) buffer may be overwritten
             float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
@@ -373,23 +458,6 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             // the warp's maximum in one instruction: non-negative floats order like their bit patterns
             amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
             if (lane == 0) s.amax[sb][warp] = amax;
-            // The previous m-block's dK product starts its way into the registers that held P-hat, under the barrier and
-            // the psi arithmetic.
-            uint32_t stage[16];
-            const bool dv_fold = kD == 256 || ((mb - 1) & 1) == 1;     // m-block it - 1 closed a dO scale block
-            // one 16-column chunk of a product buffer into the accumulators, and the next chunk set off
-#define DM_FOLD_CHUNK(ACC, SCALE, OFF)                                                                           \
-            {                                                                                                    \
-                dm::tmem_ld_wait();                                                                              \
-                _Pragma("unroll") for (int i = 0; i < 16; i += 2)                                                \
-                    dm::fma2(ACC[(OFF) + i], ACC[(OFF) + i + 1], __uint_as_float(stage[i]), __uint_as_float(stage[i + 1]), SCALE, \
-                             ACC[(OFF) + i], ACC[(OFF) + i + 1]);                                                \
-            }
-            if (it > 0) {
-                dm::mbar_wait(&s.bar_dkv_full, (it - 1) & 1, wc);
-                dm::tc_fence_after();
-                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64), stage);
-            }
             dm::named_bar_sync(1, kComputeThreads);
             if (kD == 128) {
 #pragma unroll
@@ -408,96 +476,33 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
             const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
             g_max = fmaxf(g_max, g_cur);
-            if (zh == 0) {
-                if (kD == 128) {
-                    if (tid == 0) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
-                } else if (tid == 0 || tid == 64) {    // one writer per 64-key half: psi [heads, N/64, N/64]
-                    p.psi[((int64_t)bhl * nbm + mb) * nbm + 2 * J + khalf] = tile_zero ? 0.f : psi;
+            // psi for pass 2 and the scales of this m-block's products for the fold warps.  The ring slot was last read by
+            // the fold of m-block it - kRing, which came before the products of m-block it - 2 that S^T of this one waited for.
+            if (tid == 0 || (kD == 256 && tid == 64)) {
+                s.gf[it % kRing][khalf] = g_cur;
+                if (tid == 0) s.gf[it % kRing][2] = dm::kMoInv * do8sc;
+                if (zh == 0) {
+                    if (kD == 128) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
+                    else p.psi[((int64_t)bhl * nbm + mb) * nbm + 2 * J + khalf] = tile_zero ? 0.f : psi;   // [heads, N/64, N/64]
                 }
             }
-            if (it > 0) {
-                DM_FOLD_CHUNK(dk_acc, g_prev, 0)
-                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64 + 16), stage);
-            }
 
-            // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2; the previous m-block's
-            // dK product keeps arriving in 16-column chunks between the halves
+            // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
             uint8_t* dst = s.ds[(it >> 1) & 1];       // m_lo is even: it >> 1 counts this CTA's row pairs
             {
-                uint32_t w[4];
+                uint32_t w[8];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 8; ++c) {
                     float a0, a1, a2, a3;
                     dm::mul2(a0, a1, ds[4 * c], ds[4 * c + 1], psi_inv, psi_inv);
                     dm::mul2(a2, a3, ds[4 * c + 2], ds[4 * c + 3], psi_inv, psi_inv);
                     w[c] = dm::cvt_e4m3x4(a0, a1, a2, a3);
                 }
                 *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            if (it > 0) {
-                DM_FOLD_CHUNK(dk_acc, g_prev, 16)
-                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64 + 32), stage);
-            }
-            {
-                uint32_t w[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float a0, a1, a2, a3;
-                    dm::mul2(a0, a1, ds[16 + 4 * c], ds[17 + 4 * c], psi_inv, psi_inv);
-                    dm::mul2(a2, a3, ds[18 + 4 * c], ds[19 + 4 * c], psi_inv, psi_inv);
-                    w[c] = dm::cvt_e4m3x4(a0, a1, a2, a3);
-                }
-                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
             }
             dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[sb]);
-            // ---- the rest of the previous m-block's products
-            if (it > 0) {
-                DM_FOLD_CHUNK(dk_acc, g_prev, 32)
-                dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, g * 64 + 48), stage);
-                DM_FOLD_CHUNK(dk_acc, g_prev, 48)
-                if (dv_fold) {
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        dm::tmem_ld16(dm::tmem_addr(t_dv, lane_base, g * 64 + 16 * q4), stage);
-                        DM_FOLD_CHUNK(dv_acc, f_prev, 16 * q4)
-                    }
-                }
-                dm::tc_fence_before();
-                dm::mbar_arrive_warp(&s.bar_dkv_free);
-            }
-#undef DM_FOLD_CHUNK
-            g_prev = g_cur;
-            f_prev = dm::kMoInv * do8sc;
-        }
-        if (n_it > 0) fold(n_it - 1, g_prev, f_prev);
-
-        // ---- epilogue: dK *= 1 / k8s, bf16 stores per query head
-        const float ik = 1.0f / k8s_t;
-        const int n_glob = J * 128 + key;
-        const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128 + g * 64;
-        if (p.out_fp32) {
-            float4* ok = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dk) + off);
-            float4* ov = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dv) + off);
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                ok[c] = make_float4(dk_acc[4 * c] * ik, dk_acc[4 * c + 1] * ik, dk_acc[4 * c + 2] * ik, dk_acc[4 * c + 3] * ik);
-                ov[c] = make_float4(dv_acc[4 * c], dv_acc[4 * c + 1], dv_acc[4 * c + 2], dv_acc[4 * c + 3]);
-            }
-        } else {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint32_t wk[4], wv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[8 * c + 2 * e] * ik, dk_acc[8 * c + 2 * e + 1] * ik);
-                __nv_bfloat162 b = __floats2bfloat162_rn(dv_acc[8 * c + 2 * e], dv_acc[8 * c + 2 * e + 1]);
-                wk[e] = *reinterpret_cast<uint32_t*>(&a);
-                wv[e] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            reinterpret_cast<uint4*>(p.dk + off)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
-            reinterpret_cast<uint4*>(p.dv + off)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-        }
         }
     }
     dm::tc_fence_before();
