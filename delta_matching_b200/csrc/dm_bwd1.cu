@@ -3,10 +3,13 @@
 //
 // One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  512 threads
 // in three roles that meet only through mbarriers:
-//   warps 0..7   softmax: P-hat, dS', the tile amax, psi and the two code tiles of every m-block; they hold no accumulator
-//   warps 8..11  fold: thread = key; they own dK (128 fp32 columns in registers) and drive dV's accumulator in tensor memory
-//   warps 12..15 service, one per scheduler, loops converged with one issuing lane: 12 issues the S^T / dP^T tcgen05.mma,
-//                13 the dK / dV tcgen05.mma and the dS' TMA store, 14 the TMA loads, 15 produces the per-row constants
+//   warps 0..15  softmax, four per scheduler: thread = (key, 16-row quarter of the m-block); P-hat, dS', the tile amax, psi
+//                and the two code tiles of every m-block; they hold no accumulator (64 registers each)
+//   warps 16..19 fold: thread = key; they own dK (128 fp32 columns in registers) and drive dV's accumulator in tensor memory
+//   warps 20..23 service, one per scheduler, loops converged with one issuing lane: the S^T / dP^T tcgen05.mma, the dK / dV
+//                tcgen05.mma and the dS' TMA store, the TMA loads, the per-row constants
+// Registers move between the roles by setmaxnreg; the CTA's pool is what it was launched with (768 x 80), so what the
+// softmax and service warps give up (16 x 16 + 4 x 40 per lane) is exactly what the fold warps take (4 x 104).
 // Everything is computed transposed (keys x rows): tensor-memory lane = key, so the per-key scales are per-thread
 // constants.  Per m-block:
 //   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each into one of two (S | dP) tensor-memory buffers, issued
@@ -33,8 +36,9 @@ namespace {
 
 constexpr int kTile = 128 * 128;
 constexpr int kHalf = 64 * 128;
-constexpr int kComputeThreads = 256;   // the softmax warps
-constexpr int kThreads = 512;          // two softmax warpgroups, one fold warpgroup, one service warpgroup
+constexpr int kSoftmaxWarps = 16;      // four per scheduler: key quarter (warp & 3) x 16-row quarter of the m-block (warp >> 2)
+constexpr int kComputeThreads = 32 * kSoftmaxWarps;
+constexpr int kThreads = kComputeThreads + 256;   // + one fold warpgroup + one service warpgroup
 constexpr int kRing = 4;               // depth of the per-m-block scale ring between softmax and fold warps
 
 // Geometry per head dim.  head_dim 256 (csrc/mainloop_bwd_sm90_fp8v10.hpp:1674-1761 of the reference): a code row is two
@@ -63,7 +67,7 @@ struct Bwd1Smem {
     alignas(16) float dlk[3][kGrp][64];               // -delta * k8s(group) per row
     float sc[3][2];                                   // q8sc, do8sc of the m-block (same ring)
     float gf[kRing][4];                               // per m-block: dK scale of key half 0, of key half 1, dV scale
-    float amax[2][8];
+    float amax[2][kSoftmaxWarps];
     uint64_t bar_kv, bar_qdo[kStages], bar_stage_free[kStages], bar_sp_full, bar_sp_free, bar_codes[2], bar_dkv_full[2],
         bar_dkv_free, bar_ds_free[2], bar_rows_full[3], bar_rows_free[3];
     uint32_t tmem_base;
@@ -128,12 +132,12 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::mbar_init(&s.bar_rows_free[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            dm::mbar_init(&s.bar_codes[i], 8);
+            dm::mbar_init(&s.bar_codes[i], kSoftmaxWarps);
             dm::mbar_init(&s.bar_ds_free[i], 1);
             dm::mbar_init(&s.bar_dkv_full[i], 1);
         }
         dm::mbar_init(&s.bar_sp_full, 1);
-        dm::mbar_init(&s.bar_sp_free, 8);
+        dm::mbar_init(&s.bar_sp_free, kSoftmaxWarps);
         dm::mbar_init(&s.bar_dkv_free, 4);
         dm::fence_mbar_init();
     }
@@ -149,14 +153,14 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const int key = (warp & 3) * 32 + lane;       // tensor-memory lane of the softmax and fold threads
     const int khalf = key >> 6;                   // 64-key half (the psi tile at head_dim 256)
 
-    if (warp >= 12) {
-        // =============================================================== service warps 12..15, one per scheduler
+    if (warp >= kSoftmaxWarps + 4) {
+        // =============================================================== service warps (the last warpgroup), one per scheduler
         // Each runs its loop converged (all lanes wait and compute the same addresses, so they stay in uniform registers)
         // and lane 0 alone executes the asynchronous instruction.
         dm::reg_dec<40>();
         const bool leader = lane == 0;
         const int kv_row0 = hc.bhk * p.N + J * 128;
-        if (warp == 12) {
+        if (warp == kSoftmaxWarps + 4) {
             // ---- S^T = K Q^T and dP^T = V dO^T of m-block `it`, as soon as the softmax warps have read the previous pair
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;   // descriptor strides
@@ -200,7 +204,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
-        } else if (warp == 13) {
+        } else if (warp == kSoftmaxWarps + 5) {
             // ---- dV_tmp (+)= P-hat8^T dO8 and dK_tmp = dS'8^T Q8 once the codes of m-block `it` are in shared memory and
             // the fold warps have read the previous products; the finished dS' tile of a row pair leaves by one TMA store
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
@@ -239,7 +243,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
                 if (leader) dm::tma_store_wait_all0();
             }
-        } else if (warp == 14) {
+        } else if (warp == kSoftmaxWarps + 6) {
             // ---- TMA loads: K / V once, then the Q8 / dO8 tiles of the m-blocks as far ahead as the ring allows
             const int q_row0 = hc.bh * p.rm.nq + m_lo * 64;
             if (n_it > 0 && leader) {
@@ -286,9 +290,9 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                 if (leader) dm::mbar_arrive(&s.bar_rows_full[slot]);
             }
         }
-    } else if (warp >= 8) {
+    } else if (warp >= kSoftmaxWarps) {
         // =============================================================== fold warps: thread = key, all 128 columns
-        dm::reg_inc<232>();
+        dm::reg_inc<184>();
         const int kgrp = key / kKPS;
         float dk_acc[128];
 #pragma unroll
@@ -299,30 +303,34 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::mbar_wait(&s.bar_dkv_full[it & 1], (it >> 1) & 1, wc);   // also orders the ring slot written before the codes
             dm::tc_fence_after();
             const float gk = s.gf[r][kD == 128 ? 0 : khalf], fv = s.gf[r][2];
-            uint32_t sa[32], sb[32];
-            // dK: four 32-column pieces, the next one in flight while one is added
+            uint32_t sa[16], sb[16];
+            // dK: eight 16-column pieces, the next one in flight while one is added
 #define DM_DK_PIECE(PC, CUR, NXT)                                                                                       \
             dm::tmem_ld_wait();                                                                                         \
-            if ((PC) < 3) dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, 32 * ((PC) + 1)), NXT);                           \
-            _Pragma("unroll") for (int i = 0; i < 32; i += 2)                                                            \
-                dm::fma2(dk_acc[32 * (PC) + i], dk_acc[32 * (PC) + i + 1], __uint_as_float(CUR[i]), __uint_as_float(CUR[i + 1]), gk, \
-                         dk_acc[32 * (PC) + i], dk_acc[32 * (PC) + i + 1]);
-            dm::tmem_ld32(dm::tmem_addr(t_dk, lane_base, 0), sa);
+            if ((PC) < 7) dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, 16 * ((PC) + 1)), NXT);                           \
+            _Pragma("unroll") for (int i = 0; i < 16; i += 2)                                                            \
+                dm::fma2(dk_acc[16 * (PC) + i], dk_acc[16 * (PC) + i + 1], __uint_as_float(CUR[i]), __uint_as_float(CUR[i + 1]), gk, \
+                         dk_acc[16 * (PC) + i], dk_acc[16 * (PC) + i + 1]);
+            dm::tmem_ld16(dm::tmem_addr(t_dk, lane_base, 0), sa);
             DM_DK_PIECE(0, sa, sb)
             DM_DK_PIECE(1, sb, sa)
             DM_DK_PIECE(2, sa, sb)
             DM_DK_PIECE(3, sb, sa)
+            DM_DK_PIECE(4, sa, sb)
+            DM_DK_PIECE(5, sb, sa)
+            DM_DK_PIECE(6, sa, sb)
+            DM_DK_PIECE(7, sb, sa)
 #undef DM_DK_PIECE
             // dV: the product of a whole dO scale block (two m-blocks at head_dim 128, one at 256) into the accumulator
             if (kD == 256 || (it & 1) == 1) {
 #pragma unroll
-                for (int pc = 0; pc < 4; ++pc) {
-                    dm::tmem_ld32(dm::tmem_addr(t_dv, lane_base, 32 * pc), sa);
-                    if (dv_started) dm::tmem_ld32(dm::tmem_addr(t_dva, lane_base, 32 * pc), sb);
+                for (int pc = 0; pc < 8; ++pc) {
+                    dm::tmem_ld16(dm::tmem_addr(t_dv, lane_base, 16 * pc), sa);
+                    if (dv_started) dm::tmem_ld16(dm::tmem_addr(t_dva, lane_base, 16 * pc), sb);
                     dm::tmem_ld_wait();
                     if (dv_started) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
+                        for (int i = 0; i < 16; i += 2) {
                             float y0, y1;
                             dm::fma2(y0, y1, __uint_as_float(sa[i]), __uint_as_float(sa[i + 1]), fv, __uint_as_float(sb[i]),
                                      __uint_as_float(sb[i + 1]));
@@ -331,14 +339,14 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                         }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
+                        for (int i = 0; i < 16; i += 2) {
                             float y0, y1;
                             dm::fma2(y0, y1, __uint_as_float(sa[i]), __uint_as_float(sa[i + 1]), fv, 0.f, 0.f);
                             sa[i] = __float_as_uint(y0);
                             sa[i + 1] = __float_as_uint(y1);
                         }
                     }
-                    dm::tmem_st32(dm::tmem_addr(t_dva, lane_base, 32 * pc), sa);
+                    dm::tmem_st16(dm::tmem_addr(t_dva, lane_base, 16 * pc), sa);
                 }
                 dm::tmem_st_wait();
                 dv_started = true;
@@ -352,46 +360,46 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const int n_glob = J * 128 + key;
         const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128;
 #pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-            float dvv[32];
+        for (int pc = 0; pc < 8; ++pc) {
+            float dvv[16];
             if (dv_started) {
-                dm::tmem_ld32(dm::tmem_addr(t_dva, lane_base, 32 * pc), reinterpret_cast<uint32_t*>(dvv));
+                dm::tmem_ld16(dm::tmem_addr(t_dva, lane_base, 16 * pc), reinterpret_cast<uint32_t*>(dvv));
                 dm::tmem_ld_wait();
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) dvv[i] = 0.f;
+                for (int i = 0; i < 16; ++i) dvv[i] = 0.f;
             }
             if (p.out_fp32) {
-                float4* ok = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dk) + off + 32 * pc);
-                float4* ov = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dv) + off + 32 * pc);
+                float4* ok = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dk) + off + 16 * pc);
+                float4* ov = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dv) + off + 16 * pc);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    ok[c] = make_float4(dk_acc[32 * pc + 4 * c] * ik, dk_acc[32 * pc + 4 * c + 1] * ik, dk_acc[32 * pc + 4 * c + 2] * ik,
-                                        dk_acc[32 * pc + 4 * c + 3] * ik);
+                for (int c = 0; c < 4; ++c) {
+                    ok[c] = make_float4(dk_acc[16 * pc + 4 * c] * ik, dk_acc[16 * pc + 4 * c + 1] * ik, dk_acc[16 * pc + 4 * c + 2] * ik,
+                                        dk_acc[16 * pc + 4 * c + 3] * ik);
                     ov[c] = make_float4(dvv[4 * c], dvv[4 * c + 1], dvv[4 * c + 2], dvv[4 * c + 3]);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 2; ++c) {
                     uint32_t wk[4], wv[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int i = 32 * pc + 8 * c + 2 * e;
+                        const int i = 16 * pc + 8 * c + 2 * e;
                         __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[i] * ik, dk_acc[i + 1] * ik);
                         __nv_bfloat162 b = __floats2bfloat162_rn(dvv[8 * c + 2 * e], dvv[8 * c + 2 * e + 1]);
                         wk[e] = *reinterpret_cast<uint32_t*>(&a);
                         wv[e] = *reinterpret_cast<uint32_t*>(&b);
                     }
-                    reinterpret_cast<uint4*>(p.dk + off + 32 * pc)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
-                    reinterpret_cast<uint4*>(p.dv + off + 32 * pc)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    reinterpret_cast<uint4*>(p.dk + off + 16 * pc)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+                    reinterpret_cast<uint4*>(p.dv + off + 16 * pc)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                 }
             }
         }
         dm::tc_fence_before();
     } else {
         // =============================================================== softmax warps
-        dm::reg_dec<112>();
-        const int g = warp >> 2;                      // row half: rows [32 g, 32 g + 32) of the m-block
+        dm::reg_dec<64>();
+        const int g = warp >> 2;                      // row quarter: rows [16 g, 16 g + 16) of the m-block
         const int kgrp = key / kKPS;                  // K / V scale group inside the block
         const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
@@ -410,16 +418,16 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
             // ---- phase 1: P-hat, dS', tile amax; P-hat codes to shared memory.  S^T first: the exponentials run while
             // dP^T is still on its way from tensor memory.
-            float sv[32], ds[32];
-            dm::tmem_ld32(dm::tmem_addr(tmem, lane_base, g * 32), reinterpret_cast<uint32_t*>(sv));
+            float sv[16], ds[16];
+            dm::tmem_ld16(dm::tmem_addr(tmem, lane_base, g * 16), reinterpret_cast<uint32_t*>(sv));
             dm::tmem_ld_wait();
-            dm::tmem_ld32(dm::tmem_addr(tmem + 64, lane_base, g * 32), reinterpret_cast<uint32_t*>(ds));
+            dm::tmem_ld16(dm::tmem_addr(tmem + 64, lane_base, g * 16), reinterpret_cast<uint32_t*>(ds));
             const bool diag = (mb >> 1) == diag_lb;
-            const int row_in_pair = par * 64 + g * 32;     // row offset of column 0 inside the 128-row pair
-            const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 32]);
-            const float4* dl4 = reinterpret_cast<const float4*>(&s.dlk[rb][kgrp][g * 32]);
+            const int row_in_pair = par * 64 + g * 16;     // row offset of column 0 inside the 128-row pair
+            const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 16]);
+            const float4* dl4 = reinterpret_cast<const float4*>(&s.dlk[rb][kgrp][g * 16]);
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {                // P-hat = 2^min(S dsc + rc, 12), the exponent two at a time
+            for (int c4 = 0; c4 < 4; ++c4) {                // P-hat = 2^min(S dsc + rc, 12), the exponent two at a time
                 const float4 r4 = rc4[c4];
                 const int c = 4 * c4;
                 dm::fma2(sv[c], sv[c + 1], sv[c], sv[c + 1], dsc, r4.x, r4.y);
@@ -429,7 +437,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
             if (diag) {                                     // the diagonal 128 x 128 block only: keys above the row
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
+                for (int c = 0; c < 16; ++c)
                     if (key > row_in_pair + c) sv[c] = 0.f;
             }
             dm::tmem_ld_wait();
@@ -437,7 +445,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::mbar_arrive_warp(&s.bar_sp_free);          // the (S | dP) buffer may be overwritten
             float am4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
+            for (int c4 = 0; c4 < 4; ++c4) {
                 const float4 d4 = dl4[c4];                  // -delta * k8s per row
                 const int c = 4 * c4;
                 dm::fma2(ds[c], ds[c + 1], ds[c], ds[c + 1], dpk, d4.x, d4.y);
@@ -449,22 +457,21 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
             float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
             {
-                uint32_t w[8];
+                uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) w[c] = dm::cvt_e4m3x4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
+                for (int c = 0; c < 4; ++c) w[c] = dm::cvt_e4m3x4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
                 *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(s.pt + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
             }
             // the warp's maximum in one instruction: non-negative floats order like their bit patterns
             amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
             if (lane == 0) s.amax[sb][warp] = amax;
             dm::named_bar_sync(1, kComputeThreads);
-            if (kD == 128) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, s.amax[sb][i]);
-            } else {                                   // psi tile = this thread's 64-key half: warps 2h, 2h+1 of both warpgroups
-                const int w0 = 2 * khalf;
-                amax = fmaxf(fmaxf(s.amax[sb][w0], s.amax[sb][w0 + 1]), fmaxf(s.amax[sb][w0 + 4], s.amax[sb][w0 + 5]));
+            // the tile maximum over the warps' maxima: one load per lane and one warp reduction.  head_dim 256: the psi tile is
+            // this thread's 64-key half, i.e. the warps of key quarters 2h and 2h+1 (warp & 2 selects the half)
+            {
+                const float a = s.amax[sb][lane & (kSoftmaxWarps - 1)];
+                const bool mine = kD == 128 || (((lane & 3) >> 1) == khalf);
+                amax = __uint_as_float(__reduce_max_sync(0xffffffffu, mine ? __float_as_uint(a) : 0u));
             }
             const bool tile_zero = amax * (1.0f / 448.0f) < 1e-30f;
             const float psi_raw = fmaxf(amax * (1.0f / 448.0f), 1e-30f);
@@ -473,7 +480,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             float psi = psi_raw;
             const float fl_num = g_max * (256.0f * 1e-8f);
             if (fl_num > psi_raw * q8sc * 0.99f) psi = fmaxf(psi_raw, fl_num / q8sc);
-            const float psi_inv = tile_zero ? 0.f : 1.0f / psi;
+            const float psi_inv = tile_zero ? 0.f : __frcp_rn(psi);     // the correctly rounded reciprocal, as 1 / psi
             const float g_cur = tile_zero ? 0.f : psi * dm::kMoInv * q8sc;
             g_max = fmaxf(g_max, g_cur);
             // psi for pass 2 and the scales of this m-block's products for the fold warps.  The ring slot was last read by
@@ -490,16 +497,15 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
             uint8_t* dst = s.ds[(it >> 1) & 1];       // m_lo is even: it >> 1 counts this CTA's row pairs
             {
-                uint32_t w[8];
+                uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     float a0, a1, a2, a3;
                     dm::mul2(a0, a1, ds[4 * c], ds[4 * c + 1], psi_inv, psi_inv);
                     dm::mul2(a2, a3, ds[4 * c + 2], ds[4 * c + 3], psi_inv, psi_inv);
                     w[c] = dm::cvt_e4m3x4(a0, a1, a2, a3);
                 }
                 *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair)) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(dst + dm::sw128(key, row_in_pair + 16)) = make_uint4(w[4], w[5], w[6], w[7]);
             }
             dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[sb]);
