@@ -160,15 +160,30 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
             float a = 0.f, aa = 0.f;
             const float dsc = dsc2[half], dpsc = dpsc2[half];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                float ph = dm::phat(sv[c], dsc, rc);
-                if (diag && (g * 64 + half * 32 + c > row)) ph = 0.f;
-                if (kDebug) {
-                    const float t = ph * (dp[c] * dpsc - dlt);
+            for (int c = 0; c < 32; c += 2) {               // P-hat = 2^min(S dsc + rc, 12), the exponent two at a time
+                dm::fma2(sv[c], sv[c + 1], sv[c], sv[c + 1], dsc, rc, rc);
+                sv[c] = dm::ex2(fminf(sv[c], dm::kMoE + 4.0f));
+                sv[c + 1] = dm::ex2(fminf(sv[c + 1], dm::kMoE + 4.0f));
+            }
+            if (diag) {                                     // the diagonal tile only: keys above the row
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (g * 64 + half * 32 + c > row) sv[c] = 0.f;
+            }
+            if (kDebug) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float t = sv[c] * (dp[c] * dpsc - dlt);
                     a += t;
                     aa += fabsf(t);
-                } else {
-                    a = fmaf(ph, dp[c] * dpsc, a);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    float d0, d1;
+                    dm::mul2(d0, d1, dp[c], dp[c + 1], dpsc, dpsc);
+                    a = fmaf(sv[c], d0, a);
+                    a = fmaf(sv[c + 1], d1, a);
                 }
             }
             acc += (double)(a * dm::kMoInv);
