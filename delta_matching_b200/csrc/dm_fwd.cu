@@ -15,7 +15,9 @@
 //   D_g = C_g V_g        2 x tcgen05.mma per group into zero-initialised tensor-memory temporaries, issued when the codes
 //                        are in shared memory and the previous products have been read
 //   O = O * alpha + D_0 w_0 + D_1 w_1   by the fold warps, in that order, while the softmax warps are on the next tile
-// K / V tiles arrive by TMA into a 3-stage ring.  Every mbarrier wait is bounded.
+// K / V tiles arrive by TMA into a 3-stage ring.  The kernel is persistent: one CTA per SM walks a list of (head, row
+// block) items, and since every role keeps its own place in the list, the loads and S of the next item start while the
+// softmax and fold warps finish the current one.  Every mbarrier wait is bounded.
 #include "dm_attn_common.cuh"
 #include "dm_host.h"
 
@@ -28,16 +30,16 @@ constexpr int kSoftmaxThreads = 256;
 constexpr int kRing = 4;           // depth of the per-tile row-constant ring between softmax and fold warps
 
 struct FwdSmem {
-    alignas(1024) uint8_t q[kTile];
+    alignas(1024) uint8_t q[2][kTile];             // by work item parity: the next item's Q arrives under this item's tail
     alignas(1024) uint8_t k[kStages][kTile];
     alignas(1024) uint8_t v[kStages][kTile];
     alignas(1024) uint8_t p[2][kTile];
     float gmax[2][2][128];            // [tile parity][key group][row]
     float wgt[kRing][2][128];         // [tile % kRing][key group][row]
     float alpha[kRing][128];
-    float lsum[2][128];
-    uint64_t bar_q, bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2], bar_d_full[2], bar_d_free,
-        bar_l;
+    float lsum[2][2][128];            // [work item parity][key group][row]
+    uint64_t bar_q[2], bar_q_free[2], bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2],
+        bar_d_full[2], bar_d_free, bar_l[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -51,7 +53,30 @@ struct FwdParams {
     int H, Hk, N, h0, hcount, causal;
     int* status;
     dm::RowMap rm;
+    int n_heads;                      // B * hcount: work items are (head, row block), heaviest row blocks first
 };
+
+// One work item of a persistent CTA.  Items are numbered rank-major (rank 0 = the row blocks with the most key tiles, all
+// heads, then rank 1, ...); CTA c of G takes item r G + c in even rounds r and r G + (G - 1 - c) in odd rounds, so a CTA that
+// got a long item in one round gets a short one in the next.
+struct FwdItem {
+    dm::HeadCoord hc;
+    int li, I, n_tiles;
+    bool valid;
+};
+__device__ __forceinline__ FwdItem fwd_item(const FwdParams& p, int round) {
+    FwdItem w;
+    const int G = gridDim.x, c = blockIdx.x;
+    const int nq_blk = p.rm.nq / 128;
+    const int idx = round * G + ((round & 1) ? G - 1 - c : c);
+    w.valid = idx < p.n_heads * nq_blk;
+    const int rank = idx / p.n_heads;
+    w.hc = dm::head_coord(idx - rank * p.n_heads, p.h0, p.hcount, p.H, p.Hk);
+    w.li = nq_blk - 1 - rank;
+    w.I = dm::global_block(p.rm, w.li);
+    w.n_tiles = p.causal ? w.I + 1 : p.N / 128;
+    return w;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -59,17 +84,13 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     FwdSmem& s = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
-    const int nblk = p.N / 128;
     const int nq_blk = p.rm.nq / 128;
-    const int li = nq_blk - 1 - (int)blockIdx.y;  // local row block, heaviest first
-    const int I = dm::global_block(p.rm, li);   // its place in the sequence (decides the causal extent)
-    const int n_tiles = p.causal ? I + 1 : nblk;
     dm::WaitCtx wc{&s.abort_flag, p.status};
+    // Every role walks the same list of work items; `gt` counts the key tiles of the items before the current one, so
+    // that ring stages, buffer parities and mbarrier phases run on across items (t = gt + it below).
 
     if (tid == 0) {
         s.abort_flag = 0;
-        dm::mbar_init(&s.bar_q, 1);
         for (int i = 0; i < kStages; ++i) {
             dm::mbar_init(&s.bar_kv[i], 1);
             dm::mbar_init(&s.bar_kv_free[i], 1);
@@ -79,9 +100,11 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             dm::mbar_init(&s.bar_s_free[i], 8);
             dm::mbar_init(&s.bar_codes[i], 8);
             dm::mbar_init(&s.bar_d_full[i], 1);
+            dm::mbar_init(&s.bar_q[i], 1);
+            dm::mbar_init(&s.bar_q_free[i], 1);
+            dm::mbar_init(&s.bar_l[i], 8);
         }
         dm::mbar_init(&s.bar_d_free, 4);
-        dm::mbar_init(&s.bar_l, 8);
         dm::fence_mbar_init();
         dm::tma_prefetch_desc(&tm_q);
         dm::tma_prefetch_desc(&tm_k);
@@ -99,137 +122,170 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // =============================================================== service warps
         dm::reg_dec<40>();
         const bool leader = lane == 0;
-        const int kv_row0 = hc.bhk * p.N;
         constexpr uint32_t kSub = kTile >> 4;
         if (warp == 12) {
-            // ---- S = Q K^T of tile `it` into buffer it & 1.  The code tile of the same parity is rewritten by the softmax
-            // of this tile, so the products of tile it - 2, which read it, must be complete: waiting for them here gates
-            // the softmax warps through S.
+            // ---- S = Q K^T of tile t into buffer t & 1.  The code tile of the same parity is rewritten by the softmax of
+            // this tile, so the products of tile t - 2, which read it, must be complete: waiting for them here gates the
+            // softmax warps through S.
             constexpr uint32_t idesc_s = dm::idesc_e4m3(128, 128, false, false);
-            const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q)), k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0]));
-            dm::mbar_wait(&s.bar_q, 0, wc);
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % kStages, b = it & 1;
-                dm::mbar_wait(&s.bar_kv[st], (it / kStages) & 1, wc);
-                if (it >= 2) {
-                    dm::mbar_wait(&s.bar_s_free[b], ((it - 2) >> 1) & 1, wc);
-                    dm::mbar_wait(&s.bar_d_full[b], ((it - 2) >> 1) & 1, wc);
-                }
-                dm::tc_fence_after();
-                const uint32_t ks = k_lo + st * kSub, ts = tmem + b * 128;
-                if (leader) {
-                    dm::umma_e4m3_lo<false>(ts, q_lo, ks, idesc_s);
+            const uint32_t q_lo0 = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0])), k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0]));
+            int gt = 0;
+            for (int r = 0;; ++r) {
+                const FwdItem w = fwd_item(p, r);
+                if (!w.valid) break;
+                const int qb = r & 1;
+                const uint32_t q_lo = q_lo0 + qb * kSub;
+                dm::mbar_wait(&s.bar_q[qb], (r >> 1) & 1, wc);
+                for (int it = 0; it < w.n_tiles; ++it) {
+                    const int t = gt + it, st = t % kStages, b = t & 1;
+                    dm::mbar_wait(&s.bar_kv[st], (t / kStages) & 1, wc);
+                    if (t >= 2) {
+                        dm::mbar_wait(&s.bar_s_free[b], ((t - 2) >> 1) & 1, wc);
+                        dm::mbar_wait(&s.bar_d_full[b], ((t - 2) >> 1) & 1, wc);
+                    }
+                    dm::tc_fence_after();
+                    const uint32_t ks = k_lo + st * kSub, ts = tmem + b * 128;
+                    if (leader) {
+                        dm::umma_e4m3_lo<false>(ts, q_lo, ks, idesc_s);
 #pragma unroll
-                    for (int k = 1; k < 4; ++k) dm::umma_e4m3_lo<true>(ts, q_lo + 2 * k, ks + 2 * k, idesc_s);
-                    dm::umma_commit(&s.bar_s_full[b]);
+                        for (int k = 1; k < 4; ++k) dm::umma_e4m3_lo<true>(ts, q_lo + 2 * k, ks + 2 * k, idesc_s);
+                        dm::umma_commit(&s.bar_s_full[b]);
+                        if (it == w.n_tiles - 1) dm::umma_commit(&s.bar_q_free[qb]);   // the item's Q tile has been read
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
+                gt += w.n_tiles;
             }
         } else if (warp == 13) {
-            // ---- D_g = C_g V_g for both key groups once the codes of tile `it` are in shared memory and the fold warps
-            // have read the products of tile it - 1
+            // ---- D_g = C_g V_g for both key groups once the codes of tile t are in shared memory and the fold warps
+            // have read the products of tile t - 1
             constexpr uint32_t idesc_pv = dm::idesc_e4m3(128, 128, false, true);
             const uint32_t p_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.p[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % kStages, b = it & 1;
-                dm::mbar_wait(&s.bar_kv[st], (it / kStages) & 1, wc);
-                dm::mbar_wait(&s.bar_codes[b], (it >> 1) & 1, wc);
-                if (it >= 1) dm::mbar_wait(&s.bar_d_free, (it - 1) & 1, wc);
-                dm::tc_fence_after();
-                const uint32_t pa = p_lo + b * kSub, va = v_lo + st * kSub;
-                if (leader) {
-                    // group gg: codes columns [64 gg, 64 gg + 64) (K-major, +4 per 64 bytes), V rows [64 gg, +64) (MN-major, +512)
-                    dm::umma_e4m3_lo<false>(t_d0, pa, va, idesc_pv);
-                    dm::umma_e4m3_lo<true>(t_d0, pa + 2, va + 256, idesc_pv);
-                    dm::umma_e4m3_lo<false>(t_d1, pa + 4, va + 512, idesc_pv);
-                    dm::umma_e4m3_lo<true>(t_d1, pa + 6, va + 768, idesc_pv);
-                    dm::umma_commit(&s.bar_d_full[b]);
-                    dm::umma_commit(&s.bar_kv_free[st]);       // K was read by S long ago, V just now
+            int gt = 0;
+            for (int r = 0;; ++r) {
+                const FwdItem w = fwd_item(p, r);
+                if (!w.valid) break;
+                for (int it = 0; it < w.n_tiles; ++it) {
+                    const int t = gt + it, st = t % kStages, b = t & 1;
+                    dm::mbar_wait(&s.bar_kv[st], (t / kStages) & 1, wc);
+                    dm::mbar_wait(&s.bar_codes[b], (t >> 1) & 1, wc);
+                    if (t >= 1) dm::mbar_wait(&s.bar_d_free, (t - 1) & 1, wc);
+                    dm::tc_fence_after();
+                    const uint32_t pa = p_lo + b * kSub, va = v_lo + st * kSub;
+                    if (leader) {
+                        // group gg: codes columns [64 gg, 64 gg + 64) (K-major, +4 per 64 bytes), V rows [64 gg, +64) (MN-major, +512)
+                        dm::umma_e4m3_lo<false>(t_d0, pa, va, idesc_pv);
+                        dm::umma_e4m3_lo<true>(t_d0, pa + 2, va + 256, idesc_pv);
+                        dm::umma_e4m3_lo<false>(t_d1, pa + 4, va + 512, idesc_pv);
+                        dm::umma_e4m3_lo<true>(t_d1, pa + 6, va + 768, idesc_pv);
+                        dm::umma_commit(&s.bar_d_full[b]);
+                        dm::umma_commit(&s.bar_kv_free[st]);       // K was read by S long ago, V just now
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
+                gt += w.n_tiles;
             }
         } else if (warp == 14) {
-            // ---- TMA loads: Q once, K / V tiles as far ahead as the ring allows
-            const int q_row0 = hc.bh * p.rm.nq + li * 128;
-            if (leader) {
-                dm::mbar_expect_tx(&s.bar_q, kTile);
-                dm::tma_load_2d(s.q, &tm_q, 0, q_row0, &s.bar_q);
-            }
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % kStages, j = n_tiles - 1 - it;
-                if (it >= kStages) dm::mbar_wait(&s.bar_kv_free[st], (it / kStages - 1) & 1, wc);
+            // ---- TMA loads: every item's Q, then its K / V tiles, as far ahead as the rings allow (across items too)
+            int gt = 0;
+            for (int r = 0;; ++r) {
+                const FwdItem w = fwd_item(p, r);
+                if (!w.valid) break;
+                const int qb = r & 1;
+                const int q_row0 = w.hc.bh * p.rm.nq + w.li * 128, kv_row0 = w.hc.bhk * p.N;
+                if (r >= 2) dm::mbar_wait(&s.bar_q_free[qb], ((r - 2) >> 1) & 1, wc);
                 if (leader) {
-                    dm::mbar_expect_tx(&s.bar_kv[st], 2 * kTile);
-                    dm::tma_load_2d(s.k[st], &tm_k, 0, kv_row0 + j * 128, &s.bar_kv[st]);
-                    dm::tma_load_2d(s.v[st], &tm_v, 0, kv_row0 + j * 128, &s.bar_kv[st]);
+                    dm::mbar_expect_tx(&s.bar_q[qb], kTile);
+                    dm::tma_load_2d(s.q[qb], &tm_q, 0, q_row0, &s.bar_q[qb]);
                 }
-                __syncwarp();
+                for (int it = 0; it < w.n_tiles; ++it) {
+                    const int t = gt + it, st = t % kStages, j = w.n_tiles - 1 - it;
+                    if (t >= kStages) dm::mbar_wait(&s.bar_kv_free[st], (t / kStages - 1) & 1, wc);
+                    if (leader) {
+                        dm::mbar_expect_tx(&s.bar_kv[st], 2 * kTile);
+                        dm::tma_load_2d(s.k[st], &tm_k, 0, kv_row0 + j * 128, &s.bar_kv[st]);
+                        dm::tma_load_2d(s.v[st], &tm_v, 0, kv_row0 + j * 128, &s.bar_kv[st]);
+                    }
+                    __syncwarp();
+                }
+                gt += w.n_tiles;
             }
         }
     } else if (warp >= 8) {
         // =============================================================== fold warps: thread = row, all 128 columns of O
         dm::reg_inc<208>();
         const int row = (warp & 3) * 32 + lane;
-        float o_acc[128];
+        int gt = 0;
+        for (int r = 0;; ++r) {
+            const FwdItem w = fwd_item(p, r);
+            if (!w.valid) break;
+            float o_acc[128];
 #pragma unroll
-        for (int i = 0; i < 128; ++i) o_acc[i] = 0.f;
-        for (int it = 0; it < n_tiles; ++it) {
-            const int b = it & 1, r = it % kRing;
-            dm::mbar_wait(&s.bar_d_full[b], (it >> 1) & 1, wc);      // also orders the ring slot written before the codes
-            dm::tc_fence_after();
-            const float alpha = s.alpha[r][row], w0 = s.wgt[r][0][row], w1 = s.wgt[r][1][row];
-            uint32_t sa[32], sb[32];
-            dm::tmem_ld32(dm::tmem_addr(t_d0, lane_base, 0), sa);
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+            for (int i = 0; i < 128; ++i) o_acc[i] = 0.f;
+            for (int it = 0; it < w.n_tiles; ++it) {
+                const int t = gt + it, b = t & 1, rg = t % kRing;
+                dm::mbar_wait(&s.bar_d_full[b], (t >> 1) & 1, wc);      // also orders the ring slot written before the codes
+                dm::tc_fence_after();
+                const float alpha = s.alpha[rg][row], w0 = s.wgt[rg][0][row], w1 = s.wgt[rg][1][row];
+                uint32_t sa[32], sb[32];
+                dm::tmem_ld32(dm::tmem_addr(t_d0, lane_base, 0), sa);
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-                for (int i = 0; i < 128; i += 2) dm::mul2(o_acc[i], o_acc[i + 1], o_acc[i], o_acc[i + 1], alpha, alpha);
+                    for (int i = 0; i < 128; i += 2) dm::mul2(o_acc[i], o_acc[i + 1], o_acc[i], o_acc[i + 1], alpha, alpha);
+                }
+                // eight 32-column pieces (group 0 columns 0..127, then group 1), the next one in flight while one is added
+#pragma unroll
+                for (int pc = 0; pc < 8; ++pc) {
+                    uint32_t* cur = (pc & 1) ? sb : sa;
+                    uint32_t* nxt = (pc & 1) ? sa : sb;
+                    dm::tmem_ld_wait();
+                    if (pc < 7) dm::tmem_ld32(dm::tmem_addr((pc + 1 < 4) ? t_d0 : t_d1, lane_base, 32 * ((pc + 1) & 3)), nxt);
+                    const float wg = (pc < 4) ? w0 : w1;
+                    const int c0 = 32 * (pc & 3);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        dm::fma2(o_acc[c0 + i], o_acc[c0 + i + 1], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]), wg,
+                                 o_acc[c0 + i], o_acc[c0 + i + 1]);
+                }
+                dm::tc_fence_before();
+                dm::mbar_arrive_warp(&s.bar_d_free);
             }
-            // eight 32-column pieces (group 0 columns 0..127, then group 1), the next one in flight while one is added
+            gt += w.n_tiles;
+            // ---- the item's epilogue: the softmax warps have left both halves of the denominator
+            dm::mbar_wait(&s.bar_l[r & 1], (r >> 1) & 1, wc);
+            const float l = s.lsum[r & 1][0][row] + s.lsum[r & 1][1][row];
+            const bool dead = (l == 0.f) || (l != l);
+            const float inv = dead ? 0.f : 1.0f / l;
+            const int n_glob = w.li * 128 + row;          // row inside the (local) Q-side tensors
+            __nv_bfloat16* op = p.o + (((int64_t)w.hc.b * p.rm.nq + n_glob) * p.H + w.hc.h) * 128;
 #pragma unroll
-            for (int pc = 0; pc < 8; ++pc) {
-                uint32_t* cur = (pc & 1) ? sb : sa;
-                uint32_t* nxt = (pc & 1) ? sa : sb;
-                dm::tmem_ld_wait();
-                if (pc < 7) dm::tmem_ld32(dm::tmem_addr((pc + 1 < 4) ? t_d0 : t_d1, lane_base, 32 * ((pc + 1) & 3)), nxt);
-                const float w = (pc < 4) ? w0 : w1;
-                const int c0 = 32 * (pc & 3);
+            for (int c = 0; c < 16; ++c) {
+                uint32_t w4[4];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2)
-                    dm::fma2(o_acc[c0 + i], o_acc[c0 + i + 1], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]), w, o_acc[c0 + i],
-                             o_acc[c0 + i + 1]);
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 tt = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
+                    w4[e] = *reinterpret_cast<uint32_t*>(&tt);
+                }
+                reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
-            dm::tc_fence_before();
-            dm::mbar_arrive_warp(&s.bar_d_free);
-        }
-        // ---- epilogue: the softmax warps have left both halves of the denominator
-        dm::mbar_wait(&s.bar_l, 0, wc);
-        const float l = s.lsum[0][row] + s.lsum[1][row];
-        const bool dead = (l == 0.f) || (l != l);
-        const float inv = dead ? 0.f : 1.0f / l;
-        const int n_glob = li * 128 + row;          // row inside the (local) Q-side tensors
-        __nv_bfloat16* op = p.o + (((int64_t)hc.b * p.rm.nq + n_glob) * p.H + hc.h) * 128;
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-            uint32_t w4[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 t = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
-                w4[e] = *reinterpret_cast<uint32_t*>(&t);
-            }
-            reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
         }
     } else {
         // =============================================================== softmax warps
         const int g = warp >> 2;                  // warpgroup = key group inside the tile
         const int row = (warp & 3) * 32 + lane;   // query row inside the block = tensor-memory lane
-        const float q8sc = p.q8s[(int64_t)hc.bh * nq_blk + li];
-        const float* ksp = p.k8s + (int64_t)hc.bhk * (p.N / 64) + g;
-        const float* vsp = p.v8s + (int64_t)hc.bhk * (p.N / 64) + g;
+        int gt = 0;
+        for (int r = 0;; ++r) {
+        const FwdItem w = fwd_item(p, r);
+        if (!w.valid) break;
+        const int n_tiles = w.n_tiles, I = w.I;
+        const float q8sc = p.q8s[(int64_t)w.hc.bh * nq_blk + w.li];
+        const float* ksp = p.k8s + (int64_t)w.hc.bhk * (p.N / 64) + g;
+        const float* vsp = p.v8s + (int64_t)w.hc.bhk * (p.N / 64) + g;
         float m_run = -INFINITY, l_part = 0.f;
 
         float ks_n = ksp[2 * (n_tiles - 1)], vs_n = vsp[2 * (n_tiles - 1)];
         for (int it = 0; it < n_tiles; ++it) {
-            const int j = n_tiles - 1 - it, b = it & 1, r = it % kRing;
+            const int t = gt + it, j = n_tiles - 1 - it, b = t & 1, rg = t % kRing;
             const float ks = ks_n, vs = vs_n;
             if (it + 1 < n_tiles) {
                 ks_n = ksp[2 * (j - 1)];
@@ -237,7 +293,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
 
             // ---- S for this thread's (row, key group): 64 fp32 values
-            dm::mbar_wait(&s.bar_s_full[b], (it >> 1) & 1, wc);
+            dm::mbar_wait(&s.bar_s_full[b], (t >> 1) & 1, wc);
             dm::tc_fence_after();
             float sv[64];
             dm::tmem_ld32(dm::tmem_addr(tmem + b * 128, lane_base, g * 64), reinterpret_cast<uint32_t*>(sv));
@@ -275,8 +331,8 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float sigma = dm::ex2(ms - ml2);
             // the ring slot of tile it - kRing has been read: its fold came before the fold of tile it - 3, whose release
             // of the product buffers came before the products of tile it - 2, which S of this tile waited for
-            s.wgt[r][g][row] = vs * sigma;
-            if (g == 0) s.alpha[r][row] = alpha;
+            s.wgt[rg][g][row] = vs * sigma;
+            if (g == 0) s.alpha[rg][row] = alpha;
             float part = 0.f;
             uint32_t codes[16];
             const float nms = -ms;
@@ -299,14 +355,16 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             dm::mbar_arrive_warp(&s.bar_codes[b]);
         }
 
-        // ---- epilogue: denominator halves to the fold warps, LSE
-        s.lsum[g][row] = l_part;
-        dm::mbar_arrive_warp(&s.bar_l);
+        gt += n_tiles;
+        // ---- the item's epilogue: denominator halves to the fold warps, LSE
+        s.lsum[r & 1][g][row] = l_part;
+        dm::mbar_arrive_warp(&s.bar_l[r & 1]);
         dm::named_bar_sync(1, kSoftmaxThreads);
         if (g == 0) {
-            const float l = s.lsum[0][row] + s.lsum[1][row];
+            const float l = s.lsum[r & 1][0][row] + s.lsum[r & 1][1][row];
             const bool dead = (l == 0.f) || (l != l);
-            p.lse[(int64_t)hc.bh * p.rm.nq + li * 128 + row] = dead ? -INFINITY : m_run + logf(l);
+            p.lse[(int64_t)w.hc.bh * p.rm.nq + w.li * 128 + row] = dead ? -INFINITY : m_run + logf(l);
+        }
         }
     }
     dm::tc_fence_before();
@@ -383,18 +441,29 @@ extern "C" int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, con
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     FwdParams p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status,
-                dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}};
+                dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, sh.B * hcount};
     const int smem = (int)sizeof(FwdSmem) + 1024;
+    int sms = 0;
     {
         static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
+        static int sm_count[64] = {0};
         int dev = 0;
         DM_CUDA(cudaGetDevice(&dev));
         if (dev < 0 || dev >= 64 || !attr_done[dev]) {
             DM_CUDA(cudaFuncSetAttribute(fwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            if (dev >= 0 && dev < 64) attr_done[dev] = true;
+            DM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            if (dev >= 0 && dev < 64) {
+                attr_done[dev] = true;
+                sm_count[dev] = sms;
+            }
+        } else {
+            sms = sm_count[dev];
         }
     }
-    fwd_d128_kernel<<<dim3(sh.B * hcount, cp.nq / 128), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+    // persistent: one CTA per SM walks the (head, row block) items, heaviest first
+    const int64_t items = (int64_t)sh.B * hcount * (cp.nq / 128);
+    const int grid = (int)(items < sms ? items : sms);
+    fwd_d128_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
