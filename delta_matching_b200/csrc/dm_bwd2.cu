@@ -21,13 +21,10 @@ namespace {
 constexpr int kTile = 128 * 128;
 constexpr int kStages = 3;
 
-// The dS' tiles come from HBM, the K tiles from L2 (every row block of a head reads the same ones): the dS' ring is the
-// deeper one, so that three tiles of HBM traffic are in flight per CTA within the 113 KB that let two CTAs share an SM.
-constexpr int kStagesA = 4, kStagesB = 2;
 struct Bwd2Smem {
-    alignas(1024) uint8_t a[kStagesA][kTile];  // dS' tile [key][row]
-    alignas(1024) uint8_t b[kStagesB][kTile];  // K8 tile [key][d]
-    uint64_t bar_a[kStagesA], bar_b[kStagesB], bar_mma[2];
+    alignas(1024) uint8_t a[kStages][kTile];   // dS' tile [key][row]
+    alignas(1024) uint8_t b[kStages][kTile];   // K8 tile [key][d]
+    uint64_t bar_ld[kStages], bar_mma[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -58,8 +55,7 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
 
     if (tid == 0) {
         s.abort_flag = 0;
-        for (int i = 0; i < kStagesA; ++i) dm::mbar_init(&s.bar_a[i], 1);
-        for (int i = 0; i < kStagesB; ++i) dm::mbar_init(&s.bar_b[i], 1);
+        for (int i = 0; i < kStages; ++i) dm::mbar_init(&s.bar_ld[i], 1);
         dm::mbar_init(&s.bar_mma[0], 1);
         dm::mbar_init(&s.bar_mma[1], 1);
         dm::fence_mbar_init();
@@ -74,22 +70,17 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     const int kv_row0 = hc.bhk * p.N;
     constexpr uint32_t idesc = dm::idesc_e4m3(128, 128, true, true);
 
-    auto load_a = [&](int it) {
-        const int st = it % kStagesA;
-        dm::mbar_expect_tx(&s.bar_a[st], kTile);
-        dm::tma_load_2d(s.a[st], &tm_ds, 0, (int)((tile0 + it) * 128), &s.bar_a[st]);
-    };
-    auto load_b = [&](int it) {
-        const int st = it % kStagesB;
-        dm::mbar_expect_tx(&s.bar_b[st], kTile);
-        dm::tma_load_2d(s.b[st], &tm_k, 0, kv_row0 + it * 128, &s.bar_b[st]);
+    auto load = [&](int it) {
+        const int st = it % kStages;
+        dm::mbar_expect_tx(&s.bar_ld[st], 2 * kTile);
+        dm::tma_load_2d(s.a[st], &tm_ds, 0, (int)((tile0 + it) * 128), &s.bar_ld[st]);
+        dm::tma_load_2d(s.b[st], &tm_k, 0, kv_row0 + it * 128, &s.bar_ld[st]);
     };
     auto issue = [&](int it) {
-        const int sa = it % kStagesA, sb = it % kStagesB;
-        dm::mbar_wait(&s.bar_a[sa], (it / kStagesA) & 1, wc);
-        dm::mbar_wait(&s.bar_b[sb], (it / kStagesB) & 1, wc);
+        const int st = it % kStages;
+        dm::mbar_wait(&s.bar_ld[st], (it / kStages) & 1, wc);
         dm::tc_fence_after();
-        const uint32_t aa = dm::smem_u32(s.a[sa]), ba = dm::smem_u32(s.b[sb]);
+        const uint32_t aa = dm::smem_u32(s.a[st]), ba = dm::smem_u32(s.b[st]);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
             dm::umma_e4m3(tmem + (it & 1) * 128, dm::smem_desc_sw128(aa + 4096 * k), dm::smem_desc_sw128(ba + 4096 * k), idesc, k > 0);
@@ -97,8 +88,7 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     };
 
     if (tid == 0) {
-        for (int i = 0; i < kStagesA && i < n_it; ++i) load_a(i);
-        for (int i = 0; i < kStagesB && i < n_it; ++i) load_b(i);
+        for (int i = 0; i < kStages && i < n_it; ++i) load(i);
         issue(0);
     }
 
@@ -109,27 +99,21 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
 #pragma unroll
     for (int i = 0; i < 64; ++i) dq[i] = 0.f;
 
-    float psi_next = psi_row[0];                                   // one tile ahead: the load's latency is off the loop's path
     for (int it = 0; it < n_it; ++it) {
         if (tid == 0 && it + 1 < n_it) issue(it + 1);
-        const float psi_cur = psi_next;
-        if (it + 1 < n_it) psi_next = psi_row[it + 1];
+        const float psi_cur = psi_row[it];
         const bool take = (psi_cur != 0.f) && !(psi_cur < psi_max * 1e-8f);
         dm::mbar_wait(&s.bar_mma[it & 1], (it >> 1) & 1, wc);
         dm::tc_fence_after();
-        if (tid == 0) {                                            // the MMA that read these stages is complete
-            if (it + kStagesA < n_it) load_a(it + kStagesA);
-            if (it + kStagesB < n_it) load_b(it + kStagesB);
-        }
+        if (tid == 0 && it + kStages < n_it) load(it + kStages);   // the MMA that read this stage is complete
         if (take) {                                                // warp-uniform: a warp's 32 rows share one m-block
-            float t0[32], t1[32];
-            dm::tmem_ld32(dm::tmem_addr(tmem + (it & 1) * 128, lane_base, g * 64), reinterpret_cast<uint32_t*>(t0));
-            dm::tmem_ld32(dm::tmem_addr(tmem + (it & 1) * 128, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(t1));
-            dm::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                dm::fma2(dq[i], dq[i + 1], t0[i], t0[i + 1], psi_cur, dq[i], dq[i + 1]);
-                dm::fma2(dq[32 + i], dq[33 + i], t1[i], t1[i + 1], psi_cur, dq[32 + i], dq[33 + i]);
+            for (int h = 0; h < 2; ++h) {
+                float t[32];
+                dm::tmem_ld32(dm::tmem_addr(tmem + (it & 1) * 128, lane_base, g * 64 + 32 * h), reinterpret_cast<uint32_t*>(t));
+                dm::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dq[32 * h + i] = fmaf(t[i], psi_cur, dq[32 * h + i]);
             }
             psi_max = fmaxf(psi_max, psi_cur);
         }
