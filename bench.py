@@ -216,8 +216,9 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         # NCCL announces its version on stdout at the first communicator unless told otherwise; stdout is for the one JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # (the WARN level prints it too)
+        if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "NONE"
         dist.init_process_group("nccl", device_id=dev)
 
     # count the library's kernel launches per call (one entry point can launch more than one kernel)
