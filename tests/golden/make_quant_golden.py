@@ -75,4 +75,6 @@ def golden_inputs(D):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python make_quant_golden.py <checkout of the reference project>")
+    main(sys.argv[1])
