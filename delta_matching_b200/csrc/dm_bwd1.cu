@@ -1,7 +1,7 @@
 // Pass 1 of the backward, head_dim 128: dK and dV per query head, plus the e4m3 dS' code tiles and their psi scales for
 // pass 2 (csrc/mainloop_bwd_sm90_fp8r.hpp:695-952 of the reference, restated for tcgen05).
 //
-// One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  512 threads
+// One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  768 threads
 // in three roles that meet only through mbarriers:
 //   warps 0..15  softmax, four per scheduler: thread = (key, 16-row quarter of the m-block); P-hat, dS', the tile amax, psi
 //                and the two code tiles of every m-block; they hold no accumulator (64 registers each)
@@ -12,10 +12,10 @@
 // softmax and service warps give up (16 x 16 + 4 x 40 per lane) is exactly what the fold warps take (4 x 104).
 // Everything is computed transposed (keys x rows): tensor-memory lane = key, so the per-key scales are per-thread
 // constants.  Per m-block:
-//   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each into one of two (S | dP) tensor-memory buffers, issued
-//                                  as soon as that buffer has been read, i.e. up to two m-blocks ahead
-//   compute warps                  P-hat, dS' = P-hat (dP descaled - delta k8s), tile amax over the 64 x 128 tile (one named
-//                                  barrier among the 256 compute threads), psi by the F2 / F2b rules, codes
+//   S^T = K Q^T, dP^T = V dO^T     tcgen05.mma M128 N64 K32 x 4 each into the (S | dP) tensor-memory buffer, issued as soon
+//                                  as the softmax warps have read the previous m-block's
+//   softmax warps                  P-hat, dS' = P-hat (dP descaled - delta k8s), tile amax over the 64 x 128 tile (one named
+//                                  barrier among the softmax threads), psi by the F2 / F2b rules, codes
 //                                  P-hat8 = e4m3(P-hat), dS'8 = e4m3(dS' / psi) into two swizzled K-major tiles [key][row];
 //                                  the finished 128 x 128 dS' tile of a row pair leaves by one TMA store
 //   dV_tmp (+)= P-hat8^T dO8       M128 N128 K32 x 2, zero-initialised on the first m-block of a 128-row dO scale block
