@@ -44,6 +44,12 @@ CONFIGS = {  # BASELINE.json configs: (B, N, H, Hk, D, causal, mode)
 NOMINAL_FP8_TFLOPS = 4500.0
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel, from the ncu captures summarised under profiles/
+# (attention_kernels_config2.txt, fwd_pass1_config3.txt); not re-measured by a bench run.  For pass 1 it is the compulsory
+# dS' tile write plus the Q8 / dO8 m-block tiles, which every key block of a head reads again.
+NCU_TRAFFIC_BYTES = {(2, "pass1"): 86.7e6, (3, "pass1"): 3.110e9, (2, "fwd"): 25.3e6, (3, "fwd"): 0.190e9}
+
+
 def algorithmic_flops(B, N, H, D, causal):
     return (7 if causal else 14) * B * H * N * N * D
 
@@ -446,7 +452,7 @@ def main():
                     "peak_source": "torch._scaled_mm e4m3 8192^3 best of 10, measured in this run" if fp8_peak else "nominal dense FP8",
                     "frac_of_nominal_fp8_4500": achieved / NOMINAL_FP8_TFLOPS,
                     "frac_of_measured_bf16": achieved / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
-                    "traffic": None, "kernel_ms": kernels,
+                    "traffic": NCU_TRAFFIC_BYTES.get((args.config, top)), "kernel_ms": kernels,
                     "per_kernel_tflops": {n: alg[n] / (kernels[n] * 1e-3) / 1e12 for n in cand}}
 
     cpu = None
