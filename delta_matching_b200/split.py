@@ -18,32 +18,34 @@ import torch
 
 from . import _lib
 
-_BWD_GROUPS = _os.environ.get("DM_BWD_HEAD_GROUPS", "auto").strip().lower()
-_BWD_WS_LIMIT = float(_os.environ.get("DM_BWD_WS_LIMIT_GB", "8")) * 2 ** 30
-_BWD_STREAMS = max(1, int(_os.environ.get("DM_BWD_STREAMS", "1")))
-_bwd_stream_pool = {}
+def _knob(name, default):
+    return _os.environ.get(name, default).strip()
+
+
+# The three knobs keep the reference's names and meanings; tests override the module attributes directly.
+_BWD_GROUPS = _knob("DM_BWD_HEAD_GROUPS", "auto").lower()          # auto | off (also 0, 1) | kv | head
+_BWD_WS_LIMIT = float(_knob("DM_BWD_WS_LIMIT_GB", "8")) * (1 << 30)   # bytes of dS' codes one call may hold
+_BWD_STREAMS = max(int(_knob("DM_BWD_STREAMS", "1")), 1)
+_bwd_stream_pool = {}       # (device type, index) -> side streams, made on first use and kept
 
 
 def _bwd_streams(device):
-    key = (device.type, device.index)
-    if key not in _bwd_stream_pool or len(_bwd_stream_pool[key]) < _BWD_STREAMS:
-        _bwd_stream_pool[key] = [torch.cuda.Stream(device=device) for _ in range(_BWD_STREAMS)]
-    return _bwd_stream_pool[key]
+    """The side streams of `device`, at least _BWD_STREAMS of them."""
+    have = _bwd_stream_pool.setdefault((device.type, device.index), [])
+    while len(have) < _BWD_STREAMS:
+        have.append(torch.cuda.Stream(device=device))
+    return have
 
 
 def _bwd_heads_per_call(B, H, Hkv, n_rep, N):
-    """Query heads per backward call: H (no split), n_rep (per KV group) or 1 (per head)."""
-    ws = float(B) * N * N
-    if _BWD_GROUPS in ("off", "0", "1"):
-        return H
-    if _BWD_GROUPS == "kv":
-        return n_rep
-    if _BWD_GROUPS == "head":
-        return 1
-    for hp in (H, n_rep, 1):
-        if ws * hp <= _BWD_WS_LIMIT:
-            return hp
-    return 1
+    """How many query heads one backward call covers.  A forced setting answers directly (off: all H heads, kv: the n_rep
+    heads that share a KV head, head: one); "auto" takes the widest of those three whose dS' codes, B * heads * N * N
+    bytes, stay within the limit, and one head when none does."""
+    forced = {"off": H, "0": H, "1": H, "kv": n_rep, "head": 1}.get(_BWD_GROUPS)
+    if forced is not None:
+        return forced
+    bytes_per_head = float(B) * N * N
+    return next((heads for heads in (H, n_rep) if heads * bytes_per_head <= _BWD_WS_LIMIT), 1)
 
 
 def backward_all_heads(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal):
