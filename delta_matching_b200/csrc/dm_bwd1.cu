@@ -298,6 +298,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
         for (int i = 0; i < 128; ++i) dk_acc[i] = 0.f;
         bool dv_started = false;                  // the tensor-memory accumulator holds something
+        const float ik = 1.0f / p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];   // for the epilogue; read early
         for (int it = 0; it < n_it; ++it) {
             const int r = it % kRing;
             dm::mbar_wait(&s.bar_dkv_full[it & 1], (it >> 1) & 1, wc);   // also orders the ring slot written before the codes
@@ -355,21 +356,23 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::mbar_arrive_warp(&s.bar_dkv_free);
         }
 
-        // ---- epilogue: dK *= 1 / k8s, dV from its accumulator; one row of 128 columns per thread, per query head
-        const float ik = 1.0f / p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
+        // ---- epilogue: dK *= 1 / k8s, dV from its accumulator, per query head.  A thread holds one row of 128 columns, and a
+        // store of 16 bytes per lane to 32 different rows costs the load/store unit one pass per row; so the bf16 rows go
+        // through shared memory (the K / V tiles, read for the last time by the last S^T / dP^T products; 16-byte chunks
+        // XOR-swizzled by the row so both sides are conflict-free) and leave as whole 256-byte rows, two per instruction.
         const int n_glob = J * 128 + key;
         const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128;
+        if (p.out_fp32) {
 #pragma unroll
-        for (int pc = 0; pc < 8; ++pc) {
-            float dvv[16];
-            if (dv_started) {
-                dm::tmem_ld16(dm::tmem_addr(t_dva, lane_base, 16 * pc), reinterpret_cast<uint32_t*>(dvv));
-                dm::tmem_ld_wait();
-            } else {
+            for (int pc = 0; pc < 8; ++pc) {
+                float dvv[16];
+                if (dv_started) {
+                    dm::tmem_ld16(dm::tmem_addr(t_dva, lane_base, 16 * pc), reinterpret_cast<uint32_t*>(dvv));
+                    dm::tmem_ld_wait();
+                } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) dvv[i] = 0.f;
-            }
-            if (p.out_fp32) {
+                    for (int i = 0; i < 16; ++i) dvv[i] = 0.f;
+                }
                 float4* ok = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dk) + off + 16 * pc);
                 float4* ov = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dv) + off + 16 * pc);
 #pragma unroll
@@ -378,22 +381,55 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                                         dk_acc[16 * pc + 4 * c + 3] * ik);
                     ov[c] = make_float4(dvv[4 * c], dvv[4 * c + 1], dvv[4 * c + 2], dvv[4 * c + 3]);
                 }
-            } else {
+            }
+        } else {
+            uint8_t* stg = s.k[0];                                  // 128 rows x 256 bytes
+            const int wq = warp & 3;
+            const int64_t row_stride = (int64_t)p.H * kD;           // elements between consecutive keys
+            const int64_t off0 = (((int64_t)hc.b * p.N + J * 128) * p.H + hc.h) * kD + zh * 128;
+            auto rows_out = [&](__nv_bfloat16* dst) {
+                dm::named_bar_sync(2, 128);
+#pragma unroll 4
+                for (int j = 0; j < 16; ++j) {
+                    const int row = 8 * j + 2 * wq + (lane >> 4), c = lane & 15;
+                    const uint4 w = *reinterpret_cast<const uint4*>(stg + row * 256 + ((c ^ (row & 15)) << 4));
+                    *reinterpret_cast<uint4*>(dst + off0 + row * row_stride + 8 * c) = w;
+                }
+                dm::named_bar_sync(2, 128);
+            };
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                uint32_t wk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[8 * c + 2 * e] * ik, dk_acc[8 * c + 2 * e + 1] * ik);
+                    wk[e] = *reinterpret_cast<uint32_t*>(&a);
+                }
+                *reinterpret_cast<uint4*>(stg + key * 256 + ((c ^ (key & 15)) << 4)) = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+            }
+            rows_out(p.dk);
+#pragma unroll
+            for (int pc = 0; pc < 8; ++pc) {
+                float dvv[16];
+                if (dv_started) {
+                    dm::tmem_ld16(dm::tmem_addr(t_dva, lane_base, 16 * pc), reinterpret_cast<uint32_t*>(dvv));
+                    dm::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) dvv[i] = 0.f;
+                }
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    uint32_t wk[4], wv[4];
+                    uint32_t wv[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int i = 16 * pc + 8 * c + 2 * e;
-                        __nv_bfloat162 a = __floats2bfloat162_rn(dk_acc[i] * ik, dk_acc[i + 1] * ik);
-                        __nv_bfloat162 b = __floats2bfloat162_rn(dvv[8 * c + 2 * e], dvv[8 * c + 2 * e + 1]);
-                        wk[e] = *reinterpret_cast<uint32_t*>(&a);
-                        wv[e] = *reinterpret_cast<uint32_t*>(&b);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(dvv[8 * c + 2 * e], dvv[8 * c + 2 * e + 1]);
+                        wv[e] = *reinterpret_cast<uint32_t*>(&b2);
                     }
-                    reinterpret_cast<uint4*>(p.dk + off + 16 * pc)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
-                    reinterpret_cast<uint4*>(p.dv + off + 16 * pc)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    *reinterpret_cast<uint4*>(stg + key * 256 + (((2 * pc + c) ^ (key & 15)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                 }
             }
+            rows_out(p.dv);
         }
         dm::tc_fence_before();
     } else {
