@@ -1,8 +1,9 @@
 // Pass 1 of the backward, head_dim 128: dK and dV per query head, plus the e4m3 dS' code tiles and their psi scales for
 // pass 2 (csrc/mainloop_bwd_sm90_fp8r.hpp:695-952 of the reference, restated for tcgen05).
 //
-// One CTA = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  768 threads
-// in three roles that meet only through mbarriers:
+// One work item = one 128-key block of one (batch, query head); 64-row m-blocks ascending from the causal start.  The
+// kernel is persistent: one CTA per SM walks its share of the items, and the next item starts under the tail of the
+// current one.  768 threads in three roles that meet only through mbarriers:
 //   warps 0..15  softmax, four per scheduler: thread = (key, 16-row quarter of the m-block); P-hat, dS', the tile amax, psi
 //                and the two code tiles of every m-block; they hold no accumulator (64 registers each)
 //   warps 16..19 fold: thread = key; they own dK (128 fp32 columns in registers) and drive dV's accumulator in tensor memory
@@ -63,13 +64,14 @@ struct Bwd1Smem {
     alignas(1024) uint8_t dO[kStages][kDH][kHalf];
     alignas(1024) uint8_t pt[kTile];      // P-hat codes, [key][row of the 128-row pair]; an m-block owns one 64-byte half
     alignas(1024) uint8_t ds[2][kTile];   // dS' codes, same layout, one tile per 128-row pair parity (a TMA store drains the other)
+    alignas(1024) uint8_t stg[kD == 128 ? 2 * kTile : 16];   // head_dim 128: the epilogue's 128 rows x 256 bytes of bf16 dK / dV
     alignas(16) float rc[3][64];                      // 8 - lse * log2e per row of the m-block (ring of 3 m-blocks)
     alignas(16) float dlk[3][kGrp][64];               // -delta * k8s(group) per row
     float sc[3][2];                                   // q8sc, do8sc of the m-block (same ring)
     float gf[kRing][4];                               // per m-block: dK scale of key half 0, of key half 1, dV scale
     float amax[2][kSoftmaxWarps];
     uint64_t bar_kv, bar_qdo[kStages], bar_stage_free[kStages], bar_sp_full, bar_sp_free, bar_codes[2], bar_dkv_full[2],
-        bar_dkv_free, bar_ds_free[2], bar_rows_full[3], bar_rows_free[3];
+        bar_dkv_free, bar_ds_free[2], bar_rows_full[3], bar_rows_free[3], bar_kv_free;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -89,7 +91,43 @@ struct Bwd1Params {
     int* status;
     dm::RowMap rm;                                // which rows of the sequence the Q-side tensors hold
     int out_fp32;                                 // dK / dV leave as fp32 (partials that another rank's are added to)
+    int n_heads;                                  // batch * hcount: (batch, query head) pairs of this call
 };
+
+// The work list: one item = one 128-key block J of one (batch, query head) (and one d half at head_dim 256), ordered by
+// key block, i.e. heaviest first when causal.  CTA c takes position c of the even rounds and G - 1 - c of the odd ones
+// (a snake), so the long and the short items of a round pair up.
+struct Bwd1Item {
+    dm::HeadCoord hc;
+    int J, zh, m_lo, n_it, bhl;
+    bool valid;
+};
+template <int kD>
+__device__ __forceinline__ Bwd1Item bwd1_item(const Bwd1Params& p, int round) {
+    Bwd1Item w;
+    const int G = gridDim.x, c = blockIdx.x;
+    const int nbn = p.N / 128;
+    const int idx = round * G + ((round & 1) ? G - 1 - c : c);
+    w.valid = idx < p.n_heads * nbn * (kD / 128);
+    const int jz = idx / p.n_heads;
+    w.hc = dm::head_coord(idx - jz * p.n_heads, p.h0, p.hcount, p.H, p.Hk);
+    w.bhl = w.hc.b * p.hcount + (w.hc.h - p.h0);
+    w.zh = jz / nbn;                              // d half whose dK / dV columns the item keeps (always 0 at head_dim 128)
+    w.J = jz - w.zh * nbn;
+    // m-blocks are counted in the local rows; global position grows with the local index, and both chunks of a row map
+    // start on a 128-row pair, so local and global m-block parity agree.  Causal: start at the first local m-block that is
+    // not wholly above the diagonal of key block J; a rank may hold none (n_it == 0: dK = dV = 0 for this block).
+    const int nq_blk = p.rm.nq / 128, nbm = p.rm.nq / 64;
+    w.m_lo = 0;
+    if (p.causal) {
+        const int rest = nq_blk - p.rm.half;
+        if (w.J < p.rm.off0 + p.rm.half) w.m_lo = 2 * max(w.J - p.rm.off0, 0);
+        else if (w.J < p.rm.off1 + rest) w.m_lo = 2 * (p.rm.half + max(w.J - p.rm.off1, 0));
+        else w.m_lo = nbm;
+    }
+    w.n_it = nbm - w.m_lo;
+    return w;
+}
 
 template <int kD>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -99,25 +137,14 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     extern __shared__ uint8_t smem_raw[];
     using G = Geo<kD>;
     constexpr int kDH = G::kDH, kStages = G::kStages, kGrp = G::kGrp, kKPS = G::kKeysPerScale;
-    const int zh = blockIdx.z;                    // d half whose dK / dV columns this CTA keeps (always 0 at head_dim 128)
     Bwd1Smem<kD>& s = *reinterpret_cast<Bwd1Smem<kD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const dm::HeadCoord hc = dm::head_coord(blockIdx.x, p.h0, p.hcount, p.H, p.Hk);
-    const int bhl = hc.b * p.hcount + (hc.h - p.h0);
     const int nbn = p.N / 128;
     const int nq_blk = p.rm.nq / 128, nbm = p.rm.nq / 64;   // local 128-row blocks and 64-row m-blocks
-    const int J = blockIdx.y;                     // key block; J = 0 has the most m-blocks when causal and is launched first
-    // m-blocks are counted in the local rows; global position grows with the local index, and both chunks of a row map
-    // start on a 128-row pair, so local and global m-block parity agree.  Causal: start at the first local m-block that is
-    // not wholly above the diagonal of key block J; a rank may hold none (n_it == 0: dK = dV = 0 for this block).
-    int m_lo = 0;
-    if (p.causal) {
-        const int rest = nq_blk - p.rm.half;
-        if (J < p.rm.off0 + p.rm.half) m_lo = 2 * max(J - p.rm.off0, 0);
-        else if (J < p.rm.off1 + rest) m_lo = 2 * (p.rm.half + max(J - p.rm.off1, 0));
-        else m_lo = nbm;
-    }
-    const int n_it = nbm - m_lo;
+    // Persistent: one CTA per SM walks its items (bwd1_item).  Every role keeps its own place in the list; `gt` counts the
+    // m-blocks of the items before the current one (always even), so ring stages, buffer parities and mbarrier phases
+    // run on across items (t = gt + it below) and the next item's loads, S^T / dP^T and first m-blocks run under the
+    // current item's last folds and its epilogue.  `kvn` counts the items that loaded K / V (those with m-blocks).
     dm::WaitCtx wc{&s.abort_flag, p.status};
 
     if (tid == 0) {
@@ -139,6 +166,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         dm::mbar_init(&s.bar_sp_full, 1);
         dm::mbar_init(&s.bar_sp_free, kSoftmaxWarps);
         dm::mbar_init(&s.bar_dkv_free, 4);
+        dm::mbar_init(&s.bar_kv_free, 1);
         dm::fence_mbar_init();
     }
     if (warp == 0) dm::tmem_alloc(&s.tmem_base, 512);
@@ -159,151 +187,193 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         // and lane 0 alone executes the asynchronous instruction.
         dm::reg_dec<40>();
         const bool leader = lane == 0;
-        const int kv_row0 = hc.bhk * p.N + J * 128;
         if (warp == kSoftmaxWarps + 4) {
-            // ---- S^T = K Q^T and dP^T = V dO^T of m-block `it`, as soon as the softmax warps have read the previous pair
+            // ---- S^T = K Q^T and dP^T = V dO^T of every m-block, as soon as the softmax warps have read the previous pair
             constexpr uint32_t idesc_sp = dm::idesc_e4m3(128, 64, false, false);
             constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;   // descriptor strides
             const uint32_t k_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.k[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
             const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
-            if (n_it > 0) dm::mbar_wait(&s.bar_kv, 0, wc);
-            for (int it = 0; it < n_it; ++it) {
-                const int st = it % kStages;
-                dm::mbar_wait(&s.bar_qdo[st], (it / kStages) & 1, wc);
-                // the softmax warps read the row constants of this m-block once its products are there: waiting here saves
-                // them a wait of their own
-                dm::mbar_wait(&s.bar_rows_full[it % 3], (it / 3) & 1, wc);
-                if (it >= 1) dm::mbar_wait(&s.bar_sp_free, (it - 1) & 1, wc);
-                // The softmax warps rewrite, in this m-block, the P-hat half tile that the dV product of m-block it - 2 read,
-                // and (first m-block of a row pair) the dS' tile that the TMA store of the pair two back drains: both must
-                // be done.  Gating the products gates the softmax warps.
-                if (it >= 2) dm::mbar_wait(&s.bar_dkv_full[it & 1], ((it - 2) >> 1) & 1, wc);
-                const int pair = it >> 1;           // m_lo is even: pairs start at it = 0
-                if (zh == 0 && (it & 1) == 0 && pair >= 2) dm::mbar_wait(&s.bar_ds_free[pair & 1], ((pair - 2) >> 1) & 1, wc);
-                dm::tc_fence_after();
-                const uint32_t t_s = tmem, t_dp = tmem + 64;
-                const uint32_t qs = q_lo + st * kStageQ, dos = do_lo + st * kStageQ;
-                if (leader) {
+            int gt = 0, kvn = 0;
+            for (int r = 0;; ++r) {
+                const Bwd1Item w = bwd1_item<kD>(p, r);
+                if (!w.valid) break;
+                if (w.n_it > 0) dm::mbar_wait(&s.bar_kv, kvn & 1, wc);
+                for (int it = 0; it < w.n_it; ++it) {
+                    const int t = gt + it, st = t % kStages;
+                    dm::mbar_wait(&s.bar_qdo[st], (t / kStages) & 1, wc);
+                    // the softmax warps read the row constants of this m-block once its products are there: waiting here
+                    // saves them a wait of their own
+                    dm::mbar_wait(&s.bar_rows_full[t % 3], (t / 3) & 1, wc);
+                    if (t >= 1) dm::mbar_wait(&s.bar_sp_free, (t - 1) & 1, wc);
+                    // The softmax warps rewrite, in this m-block, the P-hat half tile that the dV product of m-block t - 2 read,
+                    // and (first m-block of a row pair) the dS' tile that the TMA store of the pair two back drains: both
+                    // must be done.  Gating the products gates the softmax warps.
+                    if (t >= 2) dm::mbar_wait(&s.bar_dkv_full[t & 1], ((t - 2) >> 1) & 1, wc);
+                    const int pair = t >> 1;         // gt and m_lo are even: pairs start at even t
+                    if ((t & 1) == 0 && pair >= 2) dm::mbar_wait(&s.bar_ds_free[pair & 1], ((pair - 2) >> 1) & 1, wc);
+                    dm::tc_fence_after();
+                    const uint32_t t_s = tmem, t_dp = tmem + 64;
+                    const uint32_t qs = q_lo + st * kStageQ, dos = do_lo + st * kStageQ;
+                    if (leader) {
 #pragma unroll
-                    for (int hh = 0; hh < kDH; ++hh) {
+                        for (int hh = 0; hh < kDH; ++hh) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_s, k_lo, qs, idesc_sp);
-                            else dm::umma_e4m3_lo<true>(t_s, k_lo + hh * kSub + 2 * k, qs + hh * kSubQ + 2 * k, idesc_sp);
+                            for (int k = 0; k < 4; ++k) {
+                                if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_s, k_lo, qs, idesc_sp);
+                                else dm::umma_e4m3_lo<true>(t_s, k_lo + hh * kSub + 2 * k, qs + hh * kSubQ + 2 * k, idesc_sp);
+                            }
                         }
-                    }
 #pragma unroll
-                    for (int hh = 0; hh < kDH; ++hh) {
+                        for (int hh = 0; hh < kDH; ++hh) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_dp, v_lo, dos, idesc_sp);
-                            else dm::umma_e4m3_lo<true>(t_dp, v_lo + hh * kSub + 2 * k, dos + hh * kSubQ + 2 * k, idesc_sp);
+                            for (int k = 0; k < 4; ++k) {
+                                if ((hh | k) == 0) dm::umma_e4m3_lo<false>(t_dp, v_lo, dos, idesc_sp);
+                                else dm::umma_e4m3_lo<true>(t_dp, v_lo + hh * kSub + 2 * k, dos + hh * kSubQ + 2 * k, idesc_sp);
+                            }
                         }
+                        dm::umma_commit(&s.bar_sp_full);
+                        // K / V have been read for the last time: the loader may bring the next item's
+                        if (it == w.n_it - 1) dm::umma_commit(&s.bar_kv_free);
                     }
-                    dm::umma_commit(&s.bar_sp_full);
+                    __syncwarp();
                 }
-                __syncwarp();
+                if (w.n_it > 0) ++kvn;
+                gt += w.n_it;
             }
         } else if (warp == kSoftmaxWarps + 5) {
-            // ---- dV_tmp (+)= P-hat8^T dO8 and dK_tmp = dS'8^T Q8 once the codes of m-block `it` are in shared memory and
-            // the fold warps have read the previous products; the finished dS' tile of a row pair leaves by one TMA store
+            // ---- dV_tmp (+)= P-hat8^T dO8 and dK_tmp = dS'8^T Q8 once the codes of an m-block are in shared memory and the
+            // fold warps have read the previous products; the finished dS' tile of a row pair leaves by one TMA store
             constexpr uint32_t idesc_dkv = dm::idesc_e4m3(128, 128, false, true);
             constexpr uint32_t kSub = kTile >> 4, kSubQ = kHalf >> 4, kStageQ = (kDH * kHalf) >> 4;
             const uint32_t q_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.q[0][0])), do_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.dO[0][0]));
             const uint32_t pt_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.pt)), ds_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.ds[0]));
-            const int ds_row0 = (int)((((int64_t)bhl * nq_blk + (m_lo >> 1)) * nbn + J) * 128);   // dS' tile of the first row pair
-            for (int it = 0; it < n_it; ++it) {
-                const int st = it % kStages, par = it & 1, pp = (it >> 1) & 1;
-                dm::mbar_wait(&s.bar_codes[it & 1], (it >> 1) & 1, wc);
-                // every softmax warp is past the row constants of this m-block: their ring slot may be refilled
-                if (leader) dm::mbar_arrive(&s.bar_rows_free[it % 3]);
-                if (it >= 1) dm::mbar_wait(&s.bar_dkv_free, (it - 1) & 1, wc);
-                dm::tc_fence_after();
-                const uint32_t qs = q_lo + st * kStageQ + zh * kSubQ, dos = do_lo + st * kStageQ + zh * kSubQ;
-                const uint32_t pa = pt_lo + 4 * par, da = ds_lo + pp * kSub + 4 * par;
-                if (leader) {
-                    // head_dim 128: dV_tmp accumulates the two m-blocks of a 128-row dO scale block; head_dim 256: one m-block
-                    dm::umma_e4m3_lo_rt(t_dv, pa, dos, idesc_dkv, (kD == 128 && par != 0) ? 1u : 0u);
-                    dm::umma_e4m3_lo<true>(t_dv, pa + 2, dos + 256, idesc_dkv);
-                    dm::umma_e4m3_lo<false>(t_dk, da, qs, idesc_dkv);
-                    dm::umma_e4m3_lo<true>(t_dk, da + 2, qs + 256, idesc_dkv);
-                    dm::umma_commit(&s.bar_dkv_full[it & 1]);
-                    dm::umma_commit(&s.bar_stage_free[st]);      // the Q / dO stage has been read for the last time
-                    if (par == 1 && zh == 0) {
-                        dm::tma_store_2d(&tm_ds, 0, ds_row0 + (it >> 1) * (nbn * 128), s.ds[pp]);
-                        dm::tma_store_commit();
-                        dm::tma_store_wait_read0();
-                        dm::mbar_arrive(&s.bar_ds_free[pp]);
+            int gt = 0;
+            for (int r = 0;; ++r) {
+                const Bwd1Item w = bwd1_item<kD>(p, r);
+                if (!w.valid) break;
+                const int zh = w.zh;
+                const int ds_row0 = (int)((((int64_t)w.bhl * nq_blk + (w.m_lo >> 1)) * nbn + w.J) * 128);   // dS' tile of the first row pair
+                for (int it = 0; it < w.n_it; ++it) {
+                    const int t = gt + it, st = t % kStages, par = t & 1, pp = (t >> 1) & 1;
+                    dm::mbar_wait(&s.bar_codes[t & 1], (t >> 1) & 1, wc);
+                    // every softmax warp is past the row constants of this m-block: their ring slot may be refilled
+                    if (leader) dm::mbar_arrive(&s.bar_rows_free[t % 3]);
+                    if (t >= 1) dm::mbar_wait(&s.bar_dkv_free, (t - 1) & 1, wc);
+                    dm::tc_fence_after();
+                    const uint32_t qs = q_lo + st * kStageQ + zh * kSubQ, dos = do_lo + st * kStageQ + zh * kSubQ;
+                    const uint32_t pa = pt_lo + 4 * par, da = ds_lo + pp * kSub + 4 * par;
+                    if (leader) {
+                        // head_dim 128: dV_tmp accumulates the two m-blocks of a 128-row dO scale block; head_dim 256: one m-block
+                        dm::umma_e4m3_lo_rt(t_dv, pa, dos, idesc_dkv, (kD == 128 && par != 0) ? 1u : 0u);
+                        dm::umma_e4m3_lo<true>(t_dv, pa + 2, dos + 256, idesc_dkv);
+                        dm::umma_e4m3_lo<false>(t_dk, da, qs, idesc_dkv);
+                        dm::umma_e4m3_lo<true>(t_dk, da + 2, qs + 256, idesc_dkv);
+                        dm::umma_commit(&s.bar_dkv_full[t & 1]);
+                        dm::umma_commit(&s.bar_stage_free[st]);      // the Q / dO stage has been read for the last time
+                        if (par == 1) {
+                            // d half 1 (head_dim 256) stores nothing but arrives all the same: the phases run on across items
+                            if (zh == 0) {
+                                dm::tma_store_2d(&tm_ds, 0, ds_row0 + (it >> 1) * (nbn * 128), s.ds[pp]);
+                                dm::tma_store_commit();
+                                dm::tma_store_wait_read0();
+                            }
+                            dm::mbar_arrive(&s.bar_ds_free[pp]);
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
+                gt += w.n_it;
             }
-            if (n_it > 0) {
+            if (gt > 0) {
                 // the last products: wait so shared memory stays valid until the tensor pipe has read it
-                dm::mbar_wait(&s.bar_dkv_free, (n_it - 1) & 1, wc);
+                dm::mbar_wait(&s.bar_dkv_free, (gt - 1) & 1, wc);
                 if (leader) dm::tma_store_wait_all0();
             }
         } else if (warp == kSoftmaxWarps + 6) {
-            // ---- TMA loads: K / V once, then the Q8 / dO8 tiles of the m-blocks as far ahead as the ring allows
-            const int q_row0 = hc.bh * p.rm.nq + m_lo * 64;
-            if (n_it > 0 && leader) {
-                dm::mbar_expect_tx(&s.bar_kv, 2 * kDH * kTile);
-                for (int hh = 0; hh < kDH; ++hh) {
-                    dm::tma_load_2d(s.k[hh], &tm_k, 128 * hh, kv_row0, &s.bar_kv);
-                    dm::tma_load_2d(s.v[hh], &tm_v, 128 * hh, kv_row0, &s.bar_kv);
-                }
-            }
-            for (int it = 0; it < n_it; ++it) {
-                const int st = it % kStages;
-                if (it >= kStages) dm::mbar_wait(&s.bar_stage_free[st], (it / kStages - 1) & 1, wc);
-                if (leader) {
-                    dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
-#pragma unroll
-                    for (int hh = 0; hh < kDH; ++hh) {
-                        dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
-                        dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
+            // ---- TMA loads: an item's K / V once the previous item's last S^T / dP^T have read theirs, then the Q8 / dO8
+            // tiles of its m-blocks as far ahead as the ring allows
+            int gt = 0, kvn = 0;
+            for (int r = 0;; ++r) {
+                const Bwd1Item w = bwd1_item<kD>(p, r);
+                if (!w.valid) break;
+                const int kv_row0 = w.hc.bhk * p.N + w.J * 128;
+                const int q_row0 = w.hc.bh * p.rm.nq + w.m_lo * 64;
+                if (w.n_it > 0) {
+                    if (kvn >= 1) dm::mbar_wait(&s.bar_kv_free, (kvn - 1) & 1, wc);
+                    if (leader) {
+                        dm::mbar_expect_tx(&s.bar_kv, 2 * kDH * kTile);
+                        for (int hh = 0; hh < kDH; ++hh) {
+                            dm::tma_load_2d(s.k[hh], &tm_k, 128 * hh, kv_row0, &s.bar_kv);
+                            dm::tma_load_2d(s.v[hh], &tm_v, 128 * hh, kv_row0, &s.bar_kv);
+                        }
                     }
+                    ++kvn;
                 }
-                __syncwarp();
+                for (int it = 0; it < w.n_it; ++it) {
+                    const int t = gt + it, st = t % kStages;
+                    if (t >= kStages) dm::mbar_wait(&s.bar_stage_free[st], (t / kStages - 1) & 1, wc);
+                    if (leader) {
+                        dm::mbar_expect_tx(&s.bar_qdo[st], 2 * kDH * kHalf);
+#pragma unroll
+                        for (int hh = 0; hh < kDH; ++hh) {
+                            dm::tma_load_2d(s.q[st][hh], &tm_q, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
+                            dm::tma_load_2d(s.dO[st][hh], &tm_do, 128 * hh, q_row0 + it * 64, &s.bar_qdo[st]);
+                        }
+                    }
+                    __syncwarp();
+                }
+                gt += w.n_it;
             }
         } else {
             // ---- per-row constants of the m-blocks, three ahead: 8 - lse * log2e and -delta * k8s(group) for the 64 rows
             // (two per lane), and the Q / dO scales of the m-block
             const int nsq = kD == 128 ? nq_blk : nbm;
-            float kk[kGrp];
+            int gt = 0;
+            for (int r = 0;; ++r) {
+                const Bwd1Item w = bwd1_item<kD>(p, r);
+                if (!w.valid) break;
+                float kk[kGrp];
 #pragma unroll
-            for (int gq = 0; gq < kGrp; ++gq) kk[gq] = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + gq];
-            for (int it = 0; it < n_it; ++it) {
-                const int slot = it % 3, mb = m_lo + it;
-                const int64_t gi = (int64_t)hc.bh * p.rm.nq + (int64_t)mb * 64 + 2 * lane;
-                const float2 l2 = *reinterpret_cast<const float2*>(p.lse + gi);
-                const float2 d2 = *reinterpret_cast<const float2*>(p.delta + gi);
-                const int sq = (int)((int64_t)hc.bh * nsq) + (kD == 128 ? (mb >> 1) : mb);
-                const float sc_v = lane == 0 ? p.q8s[sq] : (lane == 1 ? p.do8s[sq] : 0.f);
-                if (it >= 3) dm::mbar_wait(&s.bar_rows_free[slot], (it / 3 - 1) & 1, wc);
-                *reinterpret_cast<float2*>(&s.rc[slot][2 * lane]) = make_float2(dm::phat_row_const(l2.x), dm::phat_row_const(l2.y));
+                for (int gq = 0; gq < kGrp; ++gq) kk[gq] = p.k8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * w.J + gq];
+                for (int it = 0; it < w.n_it; ++it) {
+                    const int t = gt + it, slot = t % 3, mb = w.m_lo + it;
+                    const int64_t gi = (int64_t)w.hc.bh * p.rm.nq + (int64_t)mb * 64 + 2 * lane;
+                    const float2 l2 = *reinterpret_cast<const float2*>(p.lse + gi);
+                    const float2 d2 = *reinterpret_cast<const float2*>(p.delta + gi);
+                    const int sq = (int)((int64_t)w.hc.bh * nsq) + (kD == 128 ? (mb >> 1) : mb);
+                    const float sc_v = lane == 0 ? p.q8s[sq] : (lane == 1 ? p.do8s[sq] : 0.f);
+                    if (t >= 3) dm::mbar_wait(&s.bar_rows_free[slot], (t / 3 - 1) & 1, wc);
+                    *reinterpret_cast<float2*>(&s.rc[slot][2 * lane]) = make_float2(dm::phat_row_const(l2.x), dm::phat_row_const(l2.y));
 #pragma unroll
-                for (int gq = 0; gq < kGrp; ++gq)
-                    *reinterpret_cast<float2*>(&s.dlk[slot][gq][2 * lane]) = make_float2(-(d2.x * kk[gq]), -(d2.y * kk[gq]));
-                if (lane < 2) s.sc[slot][lane] = sc_v;
-                __syncwarp();
-                if (leader) dm::mbar_arrive(&s.bar_rows_full[slot]);
+                    for (int gq = 0; gq < kGrp; ++gq)
+                        *reinterpret_cast<float2*>(&s.dlk[slot][gq][2 * lane]) = make_float2(-(d2.x * kk[gq]), -(d2.y * kk[gq]));
+                    if (lane < 2) s.sc[slot][lane] = sc_v;
+                    __syncwarp();
+                    if (leader) dm::mbar_arrive(&s.bar_rows_full[slot]);
+                }
+                gt += w.n_it;
             }
         }
     } else if (warp >= kSoftmaxWarps) {
         // =============================================================== fold warps: thread = key, all 128 columns
         dm::reg_inc<184>();
+        int gt = 0;
+        for (int r = 0;; ++r) {
+        const Bwd1Item w = bwd1_item<kD>(p, r);
+        if (!w.valid) break;
+        const int J = w.J, zh = w.zh, n_it = w.n_it;
+        const dm::HeadCoord hc = w.hc;
         const int kgrp = key / kKPS;
         float dk_acc[128];
 #pragma unroll
         for (int i = 0; i < 128; ++i) dk_acc[i] = 0.f;
-        bool dv_started = false;                  // the tensor-memory accumulator holds something
+        bool dv_started = false;                  // the tensor-memory accumulator holds something of this item
         const float ik = 1.0f / p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];   // for the epilogue; read early
         for (int it = 0; it < n_it; ++it) {
-            const int r = it % kRing;
-            dm::mbar_wait(&s.bar_dkv_full[it & 1], (it >> 1) & 1, wc);   // also orders the ring slot written before the codes
+            const int t = gt + it, r4 = t % kRing;
+            dm::mbar_wait(&s.bar_dkv_full[t & 1], (t >> 1) & 1, wc);   // also orders the ring slot written before the codes
             dm::tc_fence_after();
-            const float gk = s.gf[r][kD == 128 ? 0 : khalf], fv = s.gf[r][2];
+            const float gk = s.gf[r4][kD == 128 ? 0 : khalf], fv = s.gf[r4][2];
             uint32_t sa[16], sb[16];
             // dK: eight 16-column pieces, the next one in flight while one is added
 #define DM_DK_PIECE(PC, CUR, NXT)                                                                                       \
@@ -323,7 +393,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             DM_DK_PIECE(7, sb, sa)
 #undef DM_DK_PIECE
             // dV: the product of a whole dO scale block (two m-blocks at head_dim 128, one at 256) into the accumulator
-            if (kD == 256 || (it & 1) == 1) {
+            if (kD == 256 || (t & 1) == 1) {
 #pragma unroll
                 for (int pc = 0; pc < 8; ++pc) {
                     dm::tmem_ld16(dm::tmem_addr(t_dv, lane_base, 16 * pc), sa);
@@ -358,8 +428,9 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
         // ---- epilogue: dK *= 1 / k8s, dV from its accumulator, per query head.  A thread holds one row of 128 columns, and a
         // store of 16 bytes per lane to 32 different rows costs the load/store unit one pass per row; so the bf16 rows go
-        // through shared memory (the K / V tiles, read for the last time by the last S^T / dP^T products; 16-byte chunks
+        // through shared memory (a buffer of their own, since the next item's tiles are already arriving; 16-byte chunks
         // XOR-swizzled by the row so both sides are conflict-free) and leave as whole 256-byte rows, two per instruction.
+        // head_dim 256 has no room for that buffer and stores its rows directly, as the fp32 partials do.
         const int n_glob = J * 128 + key;
         const int64_t off = (((int64_t)hc.b * p.N + n_glob) * p.H + hc.h) * kD + zh * 128;
         if (p.out_fp32) {
@@ -382,8 +453,34 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
                     ov[c] = make_float4(dvv[4 * c], dvv[4 * c + 1], dvv[4 * c + 2], dvv[4 * c + 3]);
                 }
             }
+        } else if (kD == 256) {
+#pragma unroll
+            for (int pc = 0; pc < 8; ++pc) {
+                float dvv[16];
+                if (dv_started) {
+                    dm::tmem_ld16(dm::tmem_addr(t_dva, lane_base, 16 * pc), reinterpret_cast<uint32_t*>(dvv));
+                    dm::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) dvv[i] = 0.f;
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t wk[4], wv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 16 * pc + 8 * c + 2 * e;
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(dk_acc[i] * ik, dk_acc[i + 1] * ik);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(dvv[8 * c + 2 * e], dvv[8 * c + 2 * e + 1]);
+                        wk[e] = *reinterpret_cast<uint32_t*>(&a2);
+                        wv[e] = *reinterpret_cast<uint32_t*>(&b2);
+                    }
+                    reinterpret_cast<uint4*>(p.dk + off + 16 * pc)[c] = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+                    reinterpret_cast<uint4*>(p.dv + off + 16 * pc)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
         } else {
-            uint8_t* stg = s.k[0];                                  // 128 rows x 256 bytes
+            uint8_t* stg = s.stg;                                   // 128 rows x 256 bytes
             const int wq = warp & 3;
             const int64_t row_stride = (int64_t)p.H * kD;           // elements between consecutive keys
             const int64_t off0 = (((int64_t)hc.b * p.N + J * 128) * p.H + hc.h) * kD + zh * 128;
@@ -432,20 +529,27 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             rows_out(p.dv);
         }
         dm::tc_fence_before();
+        gt += n_it;
+        }
     } else {
         // =============================================================== softmax warps
         dm::reg_dec<64>();
         const int g = warp >> 2;                      // row quarter: rows [16 g, 16 g + 16) of the m-block
         const int kgrp = key / kKPS;                  // K / V scale group inside the block
-        const float k8s_t = p.k8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
-        const float v8s_t = p.v8s[(int64_t)hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
+        int gt = 0;
+        for (int r = 0;; ++r) {
+        const Bwd1Item w = bwd1_item<kD>(p, r);
+        if (!w.valid) break;
+        const int J = w.J, zh = w.zh, n_it = w.n_it, m_lo = w.m_lo, bhl = w.bhl;
+        const float k8s_t = p.k8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
+        const float v8s_t = p.v8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
         // the local 128-row block on the diagonal of this key block (none: -1); it is the first one of the causal loop
         const int diag_lb = (p.causal && n_it > 0 && dm::global_block(p.rm, m_lo >> 1) == J) ? (m_lo >> 1) : -1;
         float g_max = 0.f;
 
         for (int it = 0; it < n_it; ++it) {
-            const int mb = m_lo + it, par = mb & 1, sb = it & 1, rb = it % 3;
-            dm::mbar_wait(&s.bar_sp_full, it & 1, wc);
+            const int t = gt + it, mb = m_lo + it, par = mb & 1, sb = t & 1, rb = t % 3;
+            dm::mbar_wait(&s.bar_sp_full, t & 1, wc);
             dm::tc_fence_after();
             // the ring slot of this m-block's row constants and scales was complete before S^T / dP^T were issued
             const float q8sc = s.sc[rb][0], do8sc = s.sc[rb][1];
@@ -522,8 +626,8 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             // psi for pass 2 and the scales of this m-block's products for the fold warps.  The ring slot was last read by
             // the fold of m-block it - kRing, which came before the products of m-block it - 2 that S^T of this one waited for.
             if (tid == 0 || (kD == 256 && tid == 64)) {
-                s.gf[it % kRing][khalf] = g_cur;
-                if (tid == 0) s.gf[it % kRing][2] = dm::kMoInv * do8sc;
+                s.gf[t % kRing][khalf] = g_cur;
+                if (tid == 0) s.gf[t % kRing][2] = dm::kMoInv * do8sc;
                 if (zh == 0) {
                     if (kD == 128) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
                     else p.psi[((int64_t)bhl * nbm + mb) * nbm + 2 * J + khalf] = tile_zero ? 0.f : psi;   // [heads, N/64, N/64]
@@ -531,7 +635,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
 
             // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
-            uint8_t* dst = s.ds[(it >> 1) & 1];       // m_lo is even: it >> 1 counts this CTA's row pairs
+            uint8_t* dst = s.ds[(t >> 1) & 1];        // gt and m_lo are even: t >> 1 counts this CTA's row pairs
             {
                 uint32_t w[4];
 #pragma unroll
@@ -545,6 +649,8 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
             dm::fence_proxy_async_smem();
             dm::mbar_arrive_warp(&s.bar_codes[sb]);
+        }
+        gt += n_it;
         }
     }
     dm::tc_fence_before();
@@ -608,28 +714,30 @@ extern "C" int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
-                 sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status, dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, out_fp32};
-    if (sh.D == 128) {
-        const int smem = (int)sizeof(Bwd1Smem<128>) + 1024;
-        static bool done[64] = {false};
-        int dev = 0;
-        DM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            if (dev >= 0 && dev < 64) done[dev] = true;
+                 sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status, dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, out_fp32,
+                 sh.B * hcount};
+    // persistent: one CTA per SM walks the (key block, head[, d half]) items, heaviest first
+    static bool attr_done[64][2] = {};            // the attribute is per device and sticky: set it once per device
+    static int sm_count[64] = {0};
+    const int di = sh.D == 128 ? 0 : 1;
+    const int smem = (int)(sh.D == 128 ? sizeof(Bwd1Smem<128>) : sizeof(Bwd1Smem<256>)) + 1024;
+    int dev = 0, sms = 0;
+    DM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_done[dev][di]) {
+        if (sh.D == 128) DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        else DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        DM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (dev >= 0 && dev < 64) {
+            attr_done[dev][di] = true;
+            sm_count[dev] = sms;
         }
-        bwd1_kernel<128><<<dim3(sh.B * hcount, sh.N / 128, 1), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
     } else {
-        const int smem = (int)sizeof(Bwd1Smem<256>) + 1024;
-        static bool done[64] = {false};
-        int dev = 0;
-        DM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            if (dev >= 0 && dev < 64) done[dev] = true;
-        }
-        bwd1_kernel<256><<<dim3(sh.B * hcount, sh.N / 128, 2), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
+        sms = sm_count[dev];
     }
+    const int64_t items = (int64_t)sh.B * hcount * (sh.N / 128) * (sh.D / 128);
+    const int grid = (int)(items < sms ? items : sms);
+    if (sh.D == 128) bwd1_kernel<128><<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
+    else bwd1_kernel<256><<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
