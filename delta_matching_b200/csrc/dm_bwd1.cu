@@ -540,15 +540,19 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         for (int r = 0;; ++r) {
         const Bwd1Item w = bwd1_item<kD>(p, r);
         if (!w.valid) break;
-        const int J = w.J, zh = w.zh, n_it = w.n_it, m_lo = w.m_lo, bhl = w.bhl;
-        const float k8s_t = p.k8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
-        const float v8s_t = p.v8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * J + kgrp];
-        // the local 128-row block on the diagonal of this key block (none: -1); it is the first one of the causal loop
-        const int diag_lb = (p.causal && n_it > 0 && dm::global_block(p.rm, m_lo >> 1) == J) ? (m_lo >> 1) : -1;
+        // few values live across the m-block loop (these warps run on 64 registers): the item's psi column as a pointer,
+        // and whether its first row pair is the diagonal block of this key block (it is the first one of the causal loop)
+        const int n_it = w.n_it;
+        const float k8s_t = p.k8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * w.J + kgrp];
+        const float v8s_t = p.v8s[(int64_t)w.hc.bhk * (p.N / kKPS) + kGrp * w.J + kgrp];
+        const bool diag_item = p.causal && n_it > 0 && dm::global_block(p.rm, w.m_lo >> 1) == w.J;
+        constexpr bool kHalfPsi = kD == 256;     // psi per 64 keys: [heads, N/64, N/64]; else [heads, N/64, N/128]
+        const int psi_stride = kHalfPsi ? nbm : nbn;
+        float* psi_it = w.zh == 0 ? p.psi + ((int64_t)w.bhl * nbm + w.m_lo) * psi_stride + (kHalfPsi ? 2 * w.J + khalf : w.J) : nullptr;
         float g_max = 0.f;
 
         for (int it = 0; it < n_it; ++it) {
-            const int t = gt + it, mb = m_lo + it, par = mb & 1, sb = t & 1, rb = t % 3;
+            const int t = gt + it, par = t & 1, sb = t & 1, rb = t % 3;     // gt and m_lo are even: t has the m-block's parity
             dm::mbar_wait(&s.bar_sp_full, t & 1, wc);
             dm::tc_fence_after();
             // the ring slot of this m-block's row constants and scales was complete before S^T / dP^T were issued
@@ -562,7 +566,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             dm::tmem_ld16(dm::tmem_addr(tmem, lane_base, g * 16), reinterpret_cast<uint32_t*>(sv));
             dm::tmem_ld_wait();
             dm::tmem_ld16(dm::tmem_addr(tmem + 64, lane_base, g * 16), reinterpret_cast<uint32_t*>(ds));
-            const bool diag = (mb >> 1) == diag_lb;
+            const bool diag = diag_item && it < 2;
             const int row_in_pair = par * 64 + g * 16;     // row offset of column 0 inside the 128-row pair
             const float4* rc4 = reinterpret_cast<const float4*>(&s.rc[rb][g * 16]);
             const float4* dl4 = reinterpret_cast<const float4*>(&s.dlk[rb][kgrp][g * 16]);
@@ -628,10 +632,7 @@ bwd1_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             if (tid == 0 || (kD == 256 && tid == 64)) {
                 s.gf[t % kRing][khalf] = g_cur;
                 if (tid == 0) s.gf[t % kRing][2] = dm::kMoInv * do8sc;
-                if (zh == 0) {
-                    if (kD == 128) p.psi[((int64_t)bhl * nbm + mb) * nbn + J] = tile_zero ? 0.f : psi;
-                    else p.psi[((int64_t)bhl * nbm + mb) * nbm + 2 * J + khalf] = tile_zero ? 0.f : psi;   // [heads, N/64, N/64]
-                }
+                if (psi_it) psi_it[(int64_t)it * psi_stride] = tile_zero ? 0.f : psi;
             }
 
             // ---- phase 2: dS' codes, to shared memory for dK and to the workspace tile for pass 2
