@@ -47,7 +47,7 @@ NOMINAL_FP8_TFLOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel, from the ncu captures summarised under profiles/
 # (attention_kernels_config2.txt, fwd_pass1_config3.txt); not re-measured by a bench run.  For pass 1 it is the compulsory
 # dS' tile write plus the Q8 / dO8 m-block tiles, which every key block of a head reads again.
-NCU_TRAFFIC_BYTES = {(2, "pass1"): 86.7e6, (3, "pass1"): 3.110e9, (2, "fwd"): 25.3e6, (3, "fwd"): 0.190e9}
+NCU_TRAFFIC_BYTES = {(2, "pass1"): 82.9e6, (3, "pass1"): 3.042e9, (2, "fwd"): 25.3e6, (3, "fwd"): 0.187e9}
 
 
 def algorithmic_flops(B, N, H, D, causal):
