@@ -45,7 +45,7 @@ constexpr int kRing = 4;               // depth of the per-m-block scale ring be
 // Geometry per head dim.  head_dim 256 (csrc/mainloop_bwd_sm90_fp8v10.hpp:1674-1761 of the reference): a code row is two
 // 128-byte sub-tiles, K / V scales per 32 keys, Q / dO scales per 64-row m-block, psi per 64 rows x 64 keys (so a CTA's 128
 // keys carry two psi tiles per m-block, one per lane half), dV folded every m-block.  The dK / dV accumulators of 128 keys x
-// 256 columns do not fit the registers, so two CTAs (blockIdx.z = d half) share a key block: both form S^T / dP^T, each
+// 256 columns do not fit the registers, so two work items (d half 0 and 1) share a key block: both form S^T / dP^T, each
 // keeps its 128 columns of dK / dV, and only d half 0 writes the dS' tiles and psi.
 template <int kD>
 struct Geo {

@@ -274,16 +274,28 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int g = warp >> 2;                  // warpgroup = key group inside the tile
         const int row = (warp & 3) * 32 + lane;   // query row inside the block = tensor-memory lane
         int gt = 0;
+        // An item's Q scale and the K / V scales of its first key tile are read one item ahead: read at the item's start
+        // they would be three exposed global loads in front of its first tile.
+        float q8sc_nx = 0.f, ks_nx = 0.f, vs_nx = 0.f;
+        auto first_scales = [&](const FwdItem& wi) {
+            if (!wi.valid) return;
+            const int64_t ko = (int64_t)wi.hc.bhk * (p.N / 64) + g + 2 * (wi.n_tiles - 1);
+            q8sc_nx = p.q8s[(int64_t)wi.hc.bh * nq_blk + wi.li];
+            ks_nx = p.k8s[ko];
+            vs_nx = p.v8s[ko];
+        };
+        first_scales(fwd_item(p, 0));
         for (int r = 0;; ++r) {
         const FwdItem w = fwd_item(p, r);
         if (!w.valid) break;
         const int n_tiles = w.n_tiles, I = w.I;
-        const float q8sc = p.q8s[(int64_t)w.hc.bh * nq_blk + w.li];
+        const float q8sc = q8sc_nx;
         const float* ksp = p.k8s + (int64_t)w.hc.bhk * (p.N / 64) + g;
         const float* vsp = p.v8s + (int64_t)w.hc.bhk * (p.N / 64) + g;
         float m_run = -INFINITY, l_part = 0.f;
 
-        float ks_n = ksp[2 * (n_tiles - 1)], vs_n = vsp[2 * (n_tiles - 1)];
+        float ks_n = ks_nx, vs_n = vs_nx;
+        first_scales(fwd_item(p, r + 1));
         for (int it = 0; it < n_tiles; ++it) {
             const int t = gt + it, j = n_tiles - 1 - it, b = t & 1, rg = t % kRing;
             const float ks = ks_n, vs = vs_n;
