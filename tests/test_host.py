@@ -86,3 +86,34 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setenv("DM_SO", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="does not exist"):
         _lib.library_path()
+
+
+def _snake_items(total, ctas):
+    """The walk of the persistent kernels (bwd1_item in dm_bwd1.cu, fwd_item in dm_fwd.cu): CTA c takes position c of the
+    even rounds and ctas - 1 - c of the odd ones and stops at its first position past the end of the list."""
+    taken = []
+    for c in range(ctas):
+        mine, r = [], 0
+        while True:
+            idx = r * ctas + (ctas - 1 - c if r & 1 else c)
+            if idx >= total:
+                break
+            mine.append(idx)
+            r += 1
+        taken.append(mine)
+    return taken
+
+
+@pytest.mark.parametrize("heads,blocks,ctas", [(32, 16, 148), (128, 32, 148), (1, 512, 148), (3, 5, 148), (32, 16, 7), (1, 1, 1)])
+def test_persistent_walk_covers_every_item_once(heads, blocks, ctas):
+    """Stopping at the first invalid position loses nothing (only the last round is partial), every item is taken exactly
+    once, and with the causal weights (key block J of a head has blocks - J row pairs, items ordered by J) the heaviest
+    CTA carries at most one heaviest item more than the mean."""
+    total = heads * blocks
+    ctas = min(ctas, total)
+    taken = _snake_items(total, ctas)
+    flat = sorted(i for mine in taken for i in mine)
+    assert flat == list(range(total))
+    weight = lambda idx: blocks - idx // heads
+    loads = [sum(weight(i) for i in mine) for mine in taken]
+    assert max(loads) - sum(loads) / ctas <= blocks
