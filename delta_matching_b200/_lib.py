@@ -53,6 +53,9 @@ _SIGNATURES = {
     "dm_bwd_dbg_rowsum": (C.c_int, [_P] * 10 + [DmShape, _P, _P, _P, *_ERR]),
     "dm_probe_mma": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
     "dm_device_status": (C.c_int, [C.POINTER(C.c_int32), *_ERR]),
+    "dm_selftest_wait_timeout": (C.c_int, [_P, _P, *_ERR]),
+    "dm_init": (C.c_int, [*_ERR]),
+    "dm_register_pool_ok": (C.c_int, [C.c_int32] * 3),
     "dm_quant_qv_kpartials": (C.c_int, [_P, DmStrides, _P, DmStrides, _P, DmStrides, DmShape] + [_P] * 5 + [_P, *_ERR]),
     "dm_kmean_partials": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_kmean_fold": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
@@ -398,13 +401,30 @@ def bwd_dbg_rowsum(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, c
     return rows, rabs
 
 
-def probe_mma(a_tile, b_tile, a_mn, b_mn, n_cols=128, via_st=False):
+def probe_mma(a_tile, b_tile, a_mn, b_mn, n_cols=128, via_st=0):
+    """via_st: 0 = A by TMA, 1 = A written by threads into the swizzled tile (and echoed back by a TMA store), 2 / 3 / 4 = A
+    in tensor memory (contiguous / one K step per 32 columns / overwritten by a second product, returned as rows 128..255)."""
     dev = a_tile.device
     with torch.cuda.device(dev):
-        c = torch.empty(128, n_cols, device=dev, dtype=torch.float32)
+        c = torch.empty(256 if int(via_st) == 4 else 128, n_cols, device=dev, dtype=torch.float32)
         echo = torch.zeros(128, 128, device=dev, dtype=torch.uint8)
         _call("dm_probe_mma", _ptr(a_tile), _ptr(b_tile), int(a_mn), int(b_mn), n_cols, int(via_st), _ptr(c), _ptr(echo), _stream(dev))
     return c, echo
+
+
+def init(device=None) -> None:
+    """One-time set-up of a device (status word, kernel attributes, register-pool checks): call before capturing CUDA graphs."""
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _call("dm_init")
+
+
+def selftest_wait_timeout(device=None):
+    """Runs the bounded-wait self-test kernel; returns the two per-warp flags (1 = the wait was satisfied)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        out = torch.full((2,), -1, device=dev, dtype=torch.int32)
+        _call("dm_selftest_wait_timeout", _ptr(out), _stream(dev))
+    return out
 
 
 def device_status(device=None) -> int:

@@ -88,6 +88,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
         open(stamp, "w").write(want)
+    keep = {os.path.basename(o) for o in objs} | {os.path.basename(o)[:-2] + ".log" for o in objs} | {"link.stamp"}
+    for f in os.listdir(OBJ):          # objects of earlier source versions
+        if f not in keep:
+            os.remove(os.path.join(OBJ, f))
     return OUT
 
 

@@ -665,6 +665,21 @@ namespace dmh {
 int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen);
 }
 
+namespace dmh {
+int prepare_bwd1(char* err, size_t errlen) {
+    static DeviceOnce once;
+    return device_once(once, err, errlen, [&]() -> int {
+        DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd1Smem<128>) + 1024));
+        DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd1Smem<256>) + 1024));
+        // setmaxnreg requests: 16 softmax warps keep 64, 4 fold warps take 184, 4 service warps keep 40
+        constexpr int kPool = kComputeThreads * 64 + 128 * 184 + 128 * 40;
+        static_assert(kPool == kThreads * 80, "the roles' register requests must add up to the launch pool");
+        if (int rc = check_register_pool((const void*)bwd1_kernel<128>, kThreads, kPool, err, errlen)) return rc;
+        return check_register_pool((const void*)bwd1_kernel<256>, kThreads, kPool, err, errlen);
+    });
+}
+}  // namespace dmh
+
 extern "C" int dm_bwd_workspace_bytes(DmShape sh, int32_t hcount, size_t* ds8_bytes, size_t* psi_bytes) {
     if (!ds8_bytes || !psi_bytes || sh.N <= 0 || sh.N % 128 || sh.B <= 0 || hcount <= 0) return DM_ERR_ARG;
     const size_t kb = sh.D == 128 ? 128 : 64;
@@ -718,23 +733,10 @@ extern "C" int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v
                  sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status, dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, out_fp32,
                  sh.B * hcount};
     // persistent: one CTA per SM walks the (key block, head[, d half]) items, heaviest first
-    static bool attr_done[64][2] = {};            // the attribute is per device and sticky: set it once per device
-    static int sm_count[64] = {0};
-    const int di = sh.D == 128 ? 0 : 1;
+    if ((rc = dmh::prepare_bwd1(err, errlen))) return rc;
     const int smem = (int)(sh.D == 128 ? sizeof(Bwd1Smem<128>) : sizeof(Bwd1Smem<256>)) + 1024;
-    int dev = 0, sms = 0;
-    DM_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_done[dev][di]) {
-        if (sh.D == 128) DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        else DM_CUDA(cudaFuncSetAttribute(bwd1_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        DM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        if (dev >= 0 && dev < 64) {
-            attr_done[dev][di] = true;
-            sm_count[dev] = sms;
-        }
-    } else {
-        sms = sm_count[dev];
-    }
+    int sms = 0;
+    if ((rc = dmh::sm_count(&sms, err, errlen))) return rc;
     const int64_t items = (int64_t)sh.B * hcount * (sh.N / 128) * (sh.D / 128);
     const int grid = (int)(items < sms ? items : sms);
     if (sh.D == 128) bwd1_kernel<128><<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, ts, p);

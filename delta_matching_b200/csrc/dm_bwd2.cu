@@ -259,7 +259,16 @@ bwd2_d256_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
 
 namespace dmh {
 int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen);
+
+int prepare_bwd2(char* err, size_t errlen) {
+    static DeviceOnce once;
+    return device_once(once, err, errlen, [&]() -> int {
+        DM_CUDA(cudaFuncSetAttribute(bwd2_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd2Smem) + 1024));
+        DM_CUDA(cudaFuncSetAttribute(bwd2_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Bwd2Smem256) + 1024));
+        return DM_OK;
+    });
 }
+}  // namespace dmh
 
 extern "C" int dm_bwd_fp8_pass2(const void* ds8_ws, const float* psi_ws, const void* k8, DmShape sh, int32_t h0, int32_t hcount,
                                 void* dq, void* stream, char* err, size_t errlen) {
@@ -285,26 +294,17 @@ extern "C" int dm_bwd_fp8_pass2_cp(const void* ds8_ws, const float* psi_ws, cons
     if ((rc = dmh::make_tmap_u8(&tk, k8, sh.D, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
+    if ((rc = dmh::prepare_bwd2(err, errlen))) return rc;
     const float sm = sh.D == 128 ? 0.08838834764831845f : 0.0625f;
     Bwd2Params p{psi_ws, static_cast<__nv_bfloat16*>(dq), sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, sm / 256.0f, status,
                  dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}};
     if (sh.D == 256) {
         const int smem = (int)sizeof(Bwd2Smem256) + 1024;
-        DM_CUDA(cudaFuncSetAttribute(bwd2_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         bwd2_d256_kernel<<<dim3(sh.B * hcount, sh.N / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
         DM_CUDA(cudaGetLastError());
         return DM_OK;
     }
     const int smem = (int)sizeof(Bwd2Smem) + 1024;
-    {
-        static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
-        int dev = 0;
-        DM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(bwd2_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            if (dev >= 0 && dev < 64) attr_done[dev] = true;
-        }
-    }
     bwd2_d128_kernel<<<dim3(sh.B * hcount, cp.nq / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(ts, tk, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;

@@ -216,16 +216,8 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
     if ((rc = dmh::make_tmap_u8(&td, do8, kD, (uint64_t)sh.B * sh.H * p.rm.nq, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tk, k8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
+    if ((rc = dmh::prepare_delta(err, errlen))) return rc;
     const int smem = (int)sizeof(DeltaSmem<kD>) + 1024;
-    {
-        static bool attr_done[64] = {false};      // per template instance; the attribute is per device and sticky
-        int dev = 0;
-        DM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(delta_kernel<kDebug, kD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            if (dev >= 0 && dev < 64) attr_done[dev] = true;
-        }
-    }
     delta_kernel<kDebug, kD><<<dim3(sh.B * p.hcount, p.rm.nq / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
@@ -235,7 +227,18 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
 
 namespace dmh {
 int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen);
+
+int prepare_delta(char* err, size_t errlen) {
+    static DeviceOnce once;
+    return device_once(once, err, errlen, [&]() -> int {
+        DM_CUDA(cudaFuncSetAttribute(delta_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DeltaSmem<128>) + 1024));
+        DM_CUDA(cudaFuncSetAttribute(delta_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DeltaSmem<128>) + 1024));
+        DM_CUDA(cudaFuncSetAttribute(delta_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DeltaSmem<256>) + 1024));
+        DM_CUDA(cudaFuncSetAttribute(delta_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DeltaSmem<256>) + 1024));
+        return DM_OK;
+    });
 }
+}  // namespace dmh
 
 extern "C" int dm_delta_fp8(const void* q8, const void* k8, const void* v8, const void* do8, const float* q8s, const float* k8s,
                             const float* v8s, const float* do8s, const float* lse, DmShape sh, int32_t h0, int32_t hcount, float* delta,

@@ -384,6 +384,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp == 0) dm::tmem_dealloc(tmem, 512);
 }
 
+
 }  // namespace
 
 namespace dmh {
@@ -406,6 +407,18 @@ int launch_fwd_d256(const void* q8, const void* k8, const void* v8, const float*
 }
 
 namespace dmh {
+// setmaxnreg requests of the forward's roles: 8 softmax warps keep 128, 4 fold warps take 208, 4 service warps keep 40
+constexpr int kFwdRegPool = 256 * 128 + 128 * 208 + 128 * 40;
+static_assert(kFwdRegPool <= kThreads * 128, "the roles' register requests must fit the launch pool");
+
+int prepare_fwd(char* err, size_t errlen) {
+    static DeviceOnce once;
+    return device_once(once, err, errlen, [&]() -> int {
+        DM_CUDA(cudaFuncSetAttribute(fwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FwdSmem) + 1024));
+        return check_register_pool((const void*)fwd_d128_kernel, kThreads, kFwdRegPool, err, errlen);
+    });
+}
+
 int check_cp(const DmShape& s, const DmCp& cp, char* err, size_t errlen) {
     DM_REQUIRE(s.D == 128, DM_ERR_UNSUPPORTED, "context-parallel row maps are built for head_dim 128 only");
     DM_REQUIRE(cp.nq > 0 && cp.nq % 256 == 0 && cp.nq <= s.N, DM_ERR_ARG, "local seqlen must be a positive multiple of 256 (got %d)", cp.nq);
@@ -454,24 +467,10 @@ extern "C" int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, con
     if (!status) return DM_ERR_CUDA;
     FwdParams p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status,
                 dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, sh.B * hcount};
+    if ((rc = dmh::prepare_fwd(err, errlen))) return rc;
     const int smem = (int)sizeof(FwdSmem) + 1024;
     int sms = 0;
-    {
-        static bool attr_done[64] = {false};      // the attribute is per device and sticky: set it once per device
-        static int sm_count[64] = {0};
-        int dev = 0;
-        DM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-            DM_CUDA(cudaFuncSetAttribute(fwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            DM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-            if (dev >= 0 && dev < 64) {
-                attr_done[dev] = true;
-                sm_count[dev] = sms;
-            }
-        } else {
-            sms = sm_count[dev];
-        }
-    }
+    if ((rc = dmh::sm_count(&sms, err, errlen))) return rc;
     // persistent: one CTA per SM walks the (head, row block) items, heaviest first
     const int64_t items = (int64_t)sh.B * hcount * (cp.nq / 128);
     const int grid = (int)(items < sms ? items : sms);

@@ -246,6 +246,14 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }  // namespace
 
 namespace dmh {
+int prepare_fwd256(char* err, size_t errlen) {
+    static DeviceOnce once;
+    return device_once(once, err, errlen, [&]() -> int {
+        DM_CUDA(cudaFuncSetAttribute(fwd_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Fwd256Smem) + 1024));
+        return DM_OK;
+    });
+}
+
 int launch_fwd_d256(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s, DmShape sh,
                     int h0, int hcount, void* o, float* lse, void* stream, char* err, size_t errlen) {
     int rc;
@@ -257,7 +265,7 @@ int launch_fwd_d256(const void* q8, const void* k8, const void* v8, const float*
     if (!status) return DM_ERR_CUDA;
     Fwd256Params p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status};
     const int smem = (int)sizeof(Fwd256Smem) + 1024;
-    DM_CUDA(cudaFuncSetAttribute(fwd_d256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if ((rc = prepare_fwd256(err, errlen))) return rc;
     fwd_d256_kernel<<<dim3(sh.B * hcount, sh.N / 128), 256, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
     DM_CUDA(cudaGetLastError());
     return DM_OK;

@@ -57,6 +57,34 @@ int make_tmap_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_
     return DM_OK;
 }
 
+bool register_pool_ok(int compiled_regs_per_thread, int threads, int regs_needed) {
+    return compiled_regs_per_thread > 0 && threads > 0 && (int64_t)compiled_regs_per_thread * threads >= (int64_t)regs_needed;
+}
+
+int check_register_pool(const void* kernel, int threads, int regs_needed, char* err, size_t errlen) {
+    cudaFuncAttributes a;
+    DM_CUDA(cudaFuncGetAttributes(&a, kernel));
+    DM_REQUIRE(register_pool_ok(a.numRegs, threads, regs_needed), DM_ERR_UNSUPPORTED,
+               "this build of the kernel was compiled with %d registers per thread (%d threads), but its roles request %d in "
+               "all: refusing to launch (a setmaxnreg.inc would never be satisfied)", a.numRegs, threads, regs_needed);
+    return DM_OK;
+}
+
+int sm_count(int* sms, char* err, size_t errlen) {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    int dev = 0;
+    DM_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev >= 0 && dev < 64 && cached[dev]) {
+        *sms = cached[dev];
+        return DM_OK;
+    }
+    DM_CUDA(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+    if (dev >= 0 && dev < 64) cached[dev] = *sms;
+    return DM_OK;
+}
+
 static std::mutex g_status_mu;
 static int* g_status[64] = {nullptr};
 
@@ -83,6 +111,21 @@ int* device_status_word(char* err, size_t errlen) {
 extern "C" const char* dm_build_info(void) {
     return "libdm_b200 0.1.0; arch=sm_100a; numerics=Delta-Matching-128 v3 / Delta-Matching-256 v1 (tcgen05 realization); "
            "twins=none; bf16_dp=0; dbg=1";
+}
+
+extern "C" int dm_register_pool_ok(int32_t compiled_regs_per_thread, int32_t threads, int32_t regs_needed) {
+    return dmh::register_pool_ok(compiled_regs_per_thread, threads, regs_needed) ? 1 : 0;
+}
+
+extern "C" int dm_init(char* err, size_t errlen) {
+    if (!dmh::device_status_word(err, errlen)) return DM_ERR_CUDA;
+    int rc, sms = 0;
+    if ((rc = dmh::sm_count(&sms, err, errlen))) return rc;
+    if ((rc = dmh::prepare_fwd(err, errlen))) return rc;
+    if ((rc = dmh::prepare_fwd256(err, errlen))) return rc;
+    if ((rc = dmh::prepare_delta(err, errlen))) return rc;
+    if ((rc = dmh::prepare_bwd1(err, errlen))) return rc;
+    return dmh::prepare_bwd2(err, errlen);
 }
 
 extern "C" int dm_device_status(int32_t* status, char* err, size_t errlen) {

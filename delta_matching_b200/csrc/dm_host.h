@@ -8,6 +8,7 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include <string.h>
+#include <mutex>
 
 #include "../../include/dm_b200.h"
 
@@ -43,6 +44,40 @@ int check_device_ptr(const void* p, const char* name, char* err, size_t errlen);
 
 // 2-D uint8 tensor map: `rows` rows of `row_bytes` bytes (pitch = row_bytes), boxes of box_rows x 128 bytes, 128-byte swizzle.
 int make_tmap_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows, char* err, size_t errlen);
+
+// Kernels that move registers between their roles with setmaxnreg only work if the CTA was launched with the pool the
+// roles' requests add up to: `threads` x the compiled register count must be at least `regs_needed` (the sum over the
+// roles of threads x requested registers), otherwise a setmaxnreg.inc would wait for registers that never come.  Refuses
+// with DM_ERR_UNSUPPORTED instead of launching.
+int check_register_pool(const void* kernel, int threads, int regs_needed, char* err, size_t errlen);
+// The same rule on plain numbers (the part a host test can reach).
+bool register_pool_ok(int compiled_regs_per_thread, int threads, int regs_needed);
+
+// Per-device one-time set-up (function attributes, register-pool checks) behind a mutex: `f` runs once per device, with
+// that device current, the first time an entry point that needs it is called there (or from dm_init).
+struct DeviceOnce {
+    std::mutex mu;
+    bool done[64] = {};
+};
+template <class F>
+int device_once(DeviceOnce& o, char* err, size_t errlen, F&& f) {
+    int dev = 0;
+    DM_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(o.mu);
+    if (dev >= 0 && dev < 64 && o.done[dev]) return DM_OK;
+    if (int rc = f()) return rc;
+    if (dev >= 0 && dev < 64) o.done[dev] = true;
+    return DM_OK;
+}
+// Number of SMs of the current device (cached per device).
+int sm_count(int* sms, char* err, size_t errlen);
+
+// One-time set-up of each kernel family on the current device (also reached lazily from the entry points).
+int prepare_fwd(char* err, size_t errlen);
+int prepare_fwd256(char* err, size_t errlen);
+int prepare_delta(char* err, size_t errlen);
+int prepare_bwd1(char* err, size_t errlen);
+int prepare_bwd2(char* err, size_t errlen);
 
 // One int per device, zero-initialised: kernels write a non-zero value when a bounded wait gives up.
 int* device_status_word(char* err, size_t errlen);

@@ -56,16 +56,19 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 // Per-CTA abort state: [0] = abort flag in shared memory, status = global status word (may be null).
 struct WaitCtx {
     volatile int* abort_flag;   // shared memory
-    int* status;                // global memory, one word per launch stream of the library
+    int* status;                // global memory, one word per device (dm_device_status reads and clears it)
 };
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
-    for (uint32_t it = 0; it < DM_WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t limit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try(bar, parity)) return true;
         if ((it & 63u) == 63u && *ctx.abort_flag) return false;
     }
     *ctx.abort_flag = 1;
     if (ctx.status) atomicExch(ctx.status, (int)DM_DEV_TIMEOUT);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+    return mbar_wait_limit(bar, parity, ctx, DM_WAIT_LIMIT);
 }
 
 // Warp-level arrive: every lane has finished its part (the caller fences as needed), lane 0 arrives once for the warp.
@@ -159,6 +162,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 // TMEM address: bits 31..16 lane, bits 15..0 column.
 __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint32_t col) { return base + (lane << 16) + col; }
 
@@ -219,6 +227,19 @@ __device__ __forceinline__ void umma_e4m3_lo_rt(uint32_t d_tmem, uint32_t a_lo, 
         "mov.b64 db, {%2, %5};\n\t"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "n"(kDescHiSw128)
+        : "memory");
+}
+// The A operand read from tensor memory instead of shared memory (always K-major): lane = row of A (M = 128), each 32-bit
+// column holds four consecutive e4m3 elements of K (lowest byte first), so one K step of 32 is 8 columns and step k reads
+// columns [a_tmem + 8 k, a_tmem + 8 k + 8).  B comes from shared memory as above.
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_e4m3_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "n"(kAccumulate ? 1 : 0), "n"(kDescHiSw128)
         : "memory");
 }
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed (implies fence::before_thread_sync).

@@ -187,12 +187,37 @@ int dm_bwd_dbg_rowsum(const void* q8, const void* k8, const void* v8, const void
 /* Self-test of the tensor-core operand conventions: C[128, 128] fp32 = A * B on e4m3 tiles of 128 x 128 bytes.
  * a_mn / b_mn = 0: the tile's rows are M (or N) and its 128 bytes are K; 1: its rows are K and its 128 bytes are M (or N).
  * via_st = 1 also round-trips A through thread-written swizzled shared memory and stores it back with a TMA store into
- * `a_echo` (128 x 128 bytes).  No counterpart in the reference (its wgmma path fixes the majors in CuTe types). */
+ * `a_echo` (128 x 128 bytes).  via_st = 2, 3, 4 (a_mn = 0) put A into tensor memory with tcgen05.st and read it from there:
+ * contiguous; one K step every 32 columns; and overwritten by a second product issued right behind the first (then c_out
+ * is [256, n_cols]: the second product follows the first).  No counterpart in the reference (its wgmma path fixes the
+ * majors in CuTe types). */
 int dm_probe_mma(const void* a_tile, const void* b_tile, int32_t a_mn, int32_t b_mn, int32_t n_cols, int32_t via_st,
                  float* c_out, void* a_echo, void* stream, char* err, size_t errlen);
 
-/* Reads (and clears) the current device's status word; synchronises the device.  0 = no kernel gave up a wait. */
+/* Reads (and clears) the current device's status word; synchronises the device.  0 = no kernel gave up a wait, 1 = some
+ * wait on an mbarrier ran out of polls (the kernel then ran to its end without the data it waited for: its outputs are
+ * invalid).  Every wait in every kernel is bounded this way; nothing spins for ever.  Mirrors the lesson of the reference's
+ * pass-2 barrier bookkeeping (csrc/fq8_dq_pass2_hd128.h:323-349). */
 int dm_device_status(int32_t* status, char* err, size_t errlen);
+
+/* Self-test of that path: launches one CTA whose first warp waits, with a limit of 1024 polls, on an mbarrier nothing
+ * arrives on, and whose second warp waits on another one with the normal limit.  Both waits must come back unsatisfied
+ * (`waits_returned_ok`, two device ints, both 0), the kernel ends by itself, and the next dm_device_status reports 1, the one
+ * after that 0.  No counterpart in the reference. */
+int dm_selftest_wait_timeout(int32_t* waits_returned_ok, void* stream, char* err, size_t errlen);
+
+/* One-time set-up of the current device: allocates the status word (the library's only allocation), sets the kernels'
+ * shared-memory attributes, checks that each kernel was compiled with the register pool its roles redistribute
+ * (DM_ERR_UNSUPPORTED otherwise), caches the SM count.  Every entry point does its own part of this lazily on first use;
+ * a caller that captures CUDA graphs, or calls from several threads, calls dm_init once per device first, because the
+ * lazy set-up allocates and synchronises.  No counterpart in the reference (its ops rely on torch's lazy initialisation). */
+int dm_init(char* err, size_t errlen);
+
+/* The rule dm_init applies to the kernels that move registers between their warp roles with setmaxnreg: 1 when a kernel
+ * compiled with `compiled_regs_per_thread` registers and launched with `threads` threads owns at least the `regs_needed`
+ * registers its roles request in all, else 0 (the launch is then refused: a setmaxnreg.inc would wait for ever).  Pure host
+ * arithmetic, exported so it can be tested without a GPU.  No counterpart in the reference. */
+int dm_register_pool_ok(int32_t compiled_regs_per_thread, int32_t threads, int32_t regs_needed);
 
 #ifdef __cplusplus
 }

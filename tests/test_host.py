@@ -42,6 +42,18 @@ def test_shape_validation_happens_before_any_device_work():
     assert lib.dm_kmean_scratch_bytes(4, 8, 4096, 128) == 4 * 8 * 64 * 128 * 4
 
 
+def test_register_pool_rule():
+    """Kernels whose roles trade registers with setmaxnreg are refused unless the compiled register count times the
+    thread count covers what the roles request: pass 1 (768 threads: 16 x 32 x 64 + 128 x 184 + 128 x 40 = 768 x 80) and
+    the forward (512 threads: 256 x 128 + 128 x 208 + 128 x 40 = 512 x 128)."""
+    ok = _lib.lib().dm_register_pool_ok
+    assert ok(80, 768, 16 * 32 * 64 + 128 * 184 + 128 * 40) == 1
+    assert ok(72, 768, 16 * 32 * 64 + 128 * 184 + 128 * 40) == 0       # a compiler that found a tighter allocation
+    assert ok(128, 512, 256 * 128 + 128 * 208 + 128 * 40) == 1
+    assert ok(120, 512, 256 * 128 + 128 * 208 + 128 * 40) == 0
+    assert ok(0, 256, 1) == 0 and ok(128, 0, 1) == 0
+
+
 def test_head_group_split_decision(monkeypatch):
     monkeypatch.setattr(split, "_BWD_GROUPS", "auto")
     monkeypatch.setattr(split, "_BWD_WS_LIMIT", 8 * 2 ** 30)
