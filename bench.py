@@ -1,13 +1,17 @@
 """Benchmark of the Delta-Matching fp8 attention hot path (forward + backward, quantizers included) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 3] [--impl reference]
 
 One "step" = `o = dm_attn_func(q, k, v, causal, mode); o.backward(dO)` on one batch of synthetic input (the reference's
 own protocol, benchmarks/bench.py:52-55 of the reference: the whole composition, producers included).  The default
-workload is BASELINE config 2 (B=2, N=2048, H=16, Hk=16, D=128, causal, matched); --config 1..5 selects another.
+workload is BASELINE config 3 (B=4, N=4096, H=32, Hk=8, D=128, causal GQA, matched: the Llama-3-8B-like attention the
+metric "causal D=128" is quoted on); --config 1..5 selects another.
 Prints ONE JSON line (rank 0).  Keys:
   value        whole-job TFLOP/s over all ranks with inputs resident in HBM (algorithmic FLOPs: 7 matmuls of 2*N*N*D per
-               head, halved when causal; pass-0 recomputation and softmax work are not counted)
+               head, halved when causal; pass-0 recomputation and softmax work are not counted).  The K steps are
+               repeated until at least two seconds of GPU time have been timed, so `value` is a sustained figure with the
+               clocks sampled under it; `burst` keeps the first K steps alone and `eager_ms_per_step` the same step
+               launched from Python without the CUDA graph
   e2e          the same metric through the public API with HOST pinned buffers: H2D of q, k, v, dO and D2H of O, dQ, dK,
                dV inside the timed region
   roofline     the dominant kernel's algorithmic TFLOP/s (CUDA events around that kernel, live) against the measured dense
@@ -16,8 +20,9 @@ Prints ONE JSON line (rank 0).  Keys:
   cpu_baseline the CPU oracle (a PyTorch restatement of the reference numerics) timed on the host cores on a bounded
                sample of the same workload
 With --impl reference the CPU oracle itself is the timed arm (the reference's CUDA kernels are Hopper-only and cannot run
-here); under torchrun only rank 0 runs it.  Multi-GPU: one process per GPU, the (batch x head) work is replicated per
-rank with its own seed (weak scaling, no data-path collective), time = max over ranks.
+here); under torchrun only rank 0 runs it.  Multi-GPU: one process per GPU; by default the configuration's (batch x KV
+group) units are partitioned across the ranks with no data-path collective ("scaling": "strong"; --scaling weak gives every
+rank a whole configuration of its own instead, --scaling cp splits the sequence round an NCCL ring), time = max over ranks.
 """
 from __future__ import annotations
 
@@ -44,10 +49,18 @@ CONFIGS = {  # BASELINE.json configs: (B, N, H, Hk, D, causal, mode)
 NOMINAL_FP8_TFLOPS = 4500.0
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel, from the ncu captures summarised under profiles/
-# (attention_kernels_config2.txt, fwd_pass1_config3.txt); not re-measured by a bench run.  For pass 1 it is the compulsory
-# dS' tile write plus the Q8 / dO8 m-block tiles, which every key block of a head reads again.
-NCU_TRAFFIC_BYTES = {(2, "pass1"): 82.9e6, (3, "pass1"): 3.042e9, (2, "fwd"): 25.3e6, (3, "fwd"): 0.187e9}
+def ncu_traffic_bytes(config, kernel):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel` at BASELINE config `config`, read from the table in
+    profiles/dram_traffic.md (filled from the committed ncu captures; a bench run does not re-measure it).  None when the
+    table has no row for the pair."""
+    try:
+        for line in open(os.path.join(ROOT, "profiles", "dram_traffic.md")):
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) >= 4 and cells[0] == str(config) and cells[1] == kernel:
+                return float(cells[2]) + float(cells[3])
+    except (OSError, ValueError):
+        pass
+    return None
 
 
 def algorithmic_flops(B, N, H, D, causal):
@@ -182,18 +195,20 @@ def run_reference_arm(args, cfg, rank, world):
     line = {"impl": "reference", "metric": "fp8_attn_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e4m3", "data": "synthetic",
-            "config": workload_config(args.config, cfg, "host (CPU oracle: PyTorch restatement of the reference numerics; the "
-                                      "reference's own kernels are sm_90a-only and cannot run on this machine)"),
+            "config": workload_config(args.config, cfg),
+            "parallelism": "host (CPU oracle: PyTorch restatement of the reference numerics; the reference's own kernels are "
+                           "sm_90a-only and cannot run on this machine)",
             "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
             "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def workload_config(idx, cfg, where):
+def workload_config(idx, cfg):
+    """The workload's identity only (the same dict in both arms); how it is spread over ranks and how L2 is treated are
+    separate keys of the line."""
     B, N, H, Hk, D, causal, mode = cfg
     return {"workload": f"BASELINE config {idx}: B={B} N={N} H={H} Hk={Hk} D={D} {'causal' if causal else 'full'} {mode}, "
-                        f"fwd+bwd incl. quantizers", "B": B, "N": N, "H": H, "Hk": Hk, "D": D, "causal": causal, "mode": mode,
-            "parallelism": where, "l2": "flushed between timed iterations (256 MiB write)"}
+                        f"fwd+bwd incl. quantizers", "B": B, "N": N, "H": H, "Hk": Hk, "D": D, "causal": causal, "mode": mode}
 
 
 def main():
@@ -201,15 +216,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", type=int, default=2)
+    ap.add_argument("--config", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong", "cp"],
-                    help="weak: every rank runs the whole config (its own seed); strong: the config's (batch x KV-head) groups "
-                         "are split across the ranks (delta_matching_b200.shard), e.g. config 5 sharded over heads; cp: the "
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong", "cp"],
+                    help="strong (default): the config's (batch x KV-head) groups are partitioned across the ranks "
+                         "(delta_matching_b200.shard), e.g. config 5 sharded over heads; weak: every rank runs a whole config "
+                         "(its own seed); cp: the "
                          "sequence is split across the ranks (delta_matching_b200.cp: zig-zag chunks, K / V codes round an NCCL "
                          "ring, dK / dV partials to the key owners), head_dim 128, reported as strong scaling")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="run the timed steps eagerly instead of replaying a CUDA graph of the step")
+    ap.add_argument("--min-seconds", type=float, default=2.0, help="repeat the K timed steps until this much GPU time has been timed")
     ap.add_argument("--profile", action="store_true", help="only warm-up and timed steps (for ncu captures): no e2e, no per-kernel "
                     "timing, no peak measurement, no CPU baseline")
     args = ap.parse_args()
@@ -249,7 +266,8 @@ def main():
         return orig_call(name, *a)
     _lib._call = counting_call
 
-    if args.scaling == "strong" and world > 1:
+    scaling = args.scaling if world > 1 else "weak"     # one GPU: the whole config either way
+    if scaling == "strong":
         from delta_matching_b200.shard import kv_group_range
         first, count = kv_group_range(B, Hk, rank, world)
         rep = H // Hk
@@ -258,7 +276,7 @@ def main():
         else:
             B, Hk, H = 1, count, count * rep
         cfg = (B, N, H, Hk, D, causal, mode)          # this rank's shard; generated directly at shard size
-    cp_mode = args.scaling == "cp" and world > 1
+    cp_mode = scaling == "cp"
     cp_map = None
     if cp_mode:
         from delta_matching_b200 import cp as dmcp
@@ -315,33 +333,59 @@ def main():
     run_step = graph.replay if graph is not None else step
     sync_all()
     launches["n"] = 0
-    times = []
-    with ClockSampler(local) as clk:
-        # each step is bracketed by its own pair of events (the L2 flush between steps stays outside them); the host does
-        # not wait for a step before it enqueues the next, so the events measure the device, not the launch path
+
+    def timed_steps(fn, n):
+        """n steps, each bracketed by its own pair of events (the L2 flush between steps stays outside them); the host does
+        not wait for a step before it enqueues the next, so the events measure the device, not the launch path."""
         evs = []
-        for _ in range(args.steps):
+        for _ in range(n):
             flush.fill_(1)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            run_step()
+            fn()
             e1.record()
             evs.append((e0, e1))
         sync_all()
-        times = [a.elapsed_time(b) for a, b in evs]
-    n_launch = launches["n"] if graph is None else launches_per_step * args.steps
-    total_ms = sum(times)
-    if world > 1:
-        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        return sum(a.elapsed_time(b) for a, b in evs)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_step = total_ms / args.steps
+        return float(t.item())
+
+    # The timed region: the K steps, repeated (same K steps again) until at least --min-seconds of GPU time have been timed, so
+    # that the number is a sustained one and the clock sampler sees the GPU under load.  The first K steps alone are kept as
+    # the burst figure.  Every rank runs the same number of repeats (agreed from rank 0's burst time).
+    with ClockSampler(local) as clk:
+        burst_ms = max_over_ranks(timed_steps(run_step, args.steps))
+        repeats = 1 if args.profile else max(1, min(2000, int(-(-args.min_seconds * 1e3 // max(burst_ms, 1e-3)))))
+        if world > 1:
+            t = torch.tensor([repeats], device=dev, dtype=torch.int64)
+            dist.broadcast(t, 0)
+            repeats = int(t.item())
+        total_ms = burst_ms
+        for _ in range(repeats - 1):
+            total_ms += max_over_ranks(timed_steps(run_step, args.steps))
+    timed = args.steps * repeats
+    n_launch = launches["n"] if graph is None else launches_per_step * timed
+    ms_step = total_ms / timed
     value = world * flops / (ms_step * 1e-3) / 1e12       # every rank does `flops` (its whole config, or its equal shard)
+    burst = {"value": world * flops / (burst_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": burst_ms / args.steps,
+             "steps": args.steps}
+    # the same step launched from Python (no graph): what a caller of the API sees at small shapes
+    eager_ms = ms_step if graph is None else max_over_ranks(timed_steps(step, args.steps)) / args.steps
+    status = _lib.device_status(local)
+    if status != 0:
+        raise SystemExit(f"bench: a kernel reported a bounded-wait timeout (device status {status}); the timed numbers are void")
 
     if args.profile:
         if rank == 0:
             print(json.dumps({"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "ms_per_step": ms_step,
                               "profile_only": True, "gpu_launches": n_launch}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     # ---- end to end with host buffers: every step copies its q, k, v, dO from pinned host memory and its O, dQ, dK, dV back,
@@ -394,10 +438,7 @@ def main():
     e1.record(s_out)
     sync_all()
     e2e_ms = e0.elapsed_time(e1) / n_e2e
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(e2e_ms)
     nbytes = lambda t: t.numel() * t.element_size()
     e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": sum(nbytes(t) for t in hosts), "d2h_bytes_per_step": sum(nbytes(t) for t in outs[0]),
@@ -461,7 +502,7 @@ def main():
                     "peak_source": "torch._scaled_mm e4m3 8192^3 best of 10, measured in this run" if fp8_peak else "nominal dense FP8",
                     "frac_of_nominal_fp8_4500": achieved / NOMINAL_FP8_TFLOPS,
                     "frac_of_measured_bf16": achieved / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
-                    "traffic": NCU_TRAFFIC_BYTES.get((args.config, top)), "kernel_ms": kernels,
+                    "traffic": ncu_traffic_bytes(args.config, top), "kernel_ms": kernels,
                     "per_kernel_tflops": {n: alg[n] / (kernels[n] * 1e-3) / 1e12 for n in cand}}
 
     cpu = None
@@ -472,14 +513,15 @@ def main():
     if rank == 0:
         line = {"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-                "scaling": "strong" if cp_mode else args.scaling, "vs_baseline": None,
+                "scaling": "strong" if cp_mode else scaling, "vs_baseline": None,
+                "timed_steps": timed, "timed_seconds": total_ms * 1e-3, "burst": burst, "eager_ms_per_step": eager_ms,
                 "dtype": "e4m3", "data": "synthetic",
-                "config": workload_config(args.config, CONFIGS[args.config],
-                                          f"cp{world}: sequence split in zig-zag chunks, K / V codes round an NCCL ring, dK / dV "
-                                          f"partials to the key owners" if cp_mode else
-                                          f"dp{world} over (batch x head), no collective" +
-                                          ("; the config's KV groups split across ranks" if args.scaling == "strong" else
-                                           "; every rank runs the whole config")),
+                "config": workload_config(args.config, CONFIGS[args.config]),
+                "parallelism": (f"cp{world}: sequence split in zig-zag chunks, K / V codes round an NCCL ring, dK / dV partials to the "
+                                f"key owners" if cp_mode else f"dp{world} over (batch x KV group), no collective" +
+                                ("; the config's KV groups partitioned across the ranks" if scaling == "strong" else
+                                 "; every rank runs a whole config of its own")),
+                "l2": "flushed between timed iterations (256 MiB write)",
                 "tflops_per_gpu": value / world, "frac_of_nominal_fp8_per_gpu": value / world / NOMINAL_FP8_TFLOPS,
                 "clocks": clk.summary(), "e2e": e2e, "gpu_launches": n_launch,
                 "step_launch": "CUDA graph replay of one captured step" if graph is not None else "eager", "roofline": roof, "cpu_baseline": cpu}

@@ -1,6 +1,6 @@
 """Context parallelism for long sequences: the sequence is split across the ranks of a process group, one GPU each.
 
-The reference has no sequence parallelism (its long-context tool is the head split of flash_attn_interface.py:331-420);
+The reference has no sequence parallelism (its long-context tool is the head split of delta_matching/split.py:17-92);
 this module is the ring that the 65536-token configuration runs on at 8 GPUs.  head_dim 128 only.
 
 Layout.  With W ranks the sequence is cut into 2W chunks of c = N / (2W) rows and rank r holds chunks r and 2W-1-r
