@@ -29,10 +29,39 @@ struct RowMap {
 };
 __device__ __forceinline__ int global_block(const RowMap& m, int li) { return li < m.half ? m.off0 + li : m.off1 + (li - m.half); }
 
+// Division by a run-time constant without the divide sequence (about thirty dependent instructions per quotient, paid by every
+// role of a persistent kernel at every work item): q = (t + ((x - t) >> s1)) >> s2 with t = mulhi(x, m), exact for every
+// 32-bit x and d >= 1 (round-up method of Granlund and Montgomery).  The host fills the constants.
+struct FastDiv {
+    uint32_t d, m, s1, s2;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f{d, 1u, 0u, 0u};
+    uint32_t l = 0;
+    while ((uint64_t(1) << l) < d) ++l;                          // l = ceil(log2 d)
+    f.m = (uint32_t)(((uint64_t(1) << 32) * ((uint64_t(1) << l) - d)) / d + 1);
+    f.s1 = l < 1 ? l : 1;
+    f.s2 = l < 1 ? 0 : l - 1;
+    return f;
+}
+__device__ __forceinline__ uint32_t fdiv(uint32_t x, const FastDiv& f) {
+    const uint32_t t = __umulhi(x, f.m);
+    return (t + ((x - t) >> f.s1)) >> f.s2;
+}
+
 // Problem coordinates of one CTA.
 struct HeadCoord {
     int b, h, bh, bhk;
 };
+// The same with the two divisors (hcount, H / Hk) prepared by the host.
+__device__ __forceinline__ HeadCoord head_coord(int y, int h0, const FastDiv& hcount, int H, int Hk, const FastDiv& rep) {
+    HeadCoord c;
+    c.b = (int)fdiv((uint32_t)y, hcount);
+    c.h = h0 + y - c.b * (int)hcount.d;
+    c.bh = c.b * H + c.h;
+    c.bhk = c.b * Hk + (int)fdiv((uint32_t)c.h, rep);
+    return c;
+}
 __device__ __forceinline__ HeadCoord head_coord(int y, int h0, int hcount, int H, int Hk) {
     HeadCoord c;
     c.b = y / hcount;

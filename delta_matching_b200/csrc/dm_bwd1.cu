@@ -92,6 +92,7 @@ struct Bwd1Params {
     dm::RowMap rm;                                // which rows of the sequence the Q-side tensors hold
     int out_fp32;                                 // dK / dV leave as fp32 (partials that another rank's are added to)
     int n_heads;                                  // batch * hcount: (batch, query head) pairs of this call
+    dm::FastDiv fd_heads, fd_hcount, fd_rep, fd_nbn;   // divisions by n_heads, hcount, H / Hk and N / 128
 };
 
 // The work list: one item = one 128-key block J of one (batch, query head) (and one d half at head_dim 256), ordered by
@@ -109,10 +110,10 @@ __device__ __forceinline__ Bwd1Item bwd1_item(const Bwd1Params& p, int round) {
     const int nbn = p.N / 128;
     const int idx = round * G + ((round & 1) ? G - 1 - c : c);
     w.valid = idx < p.n_heads * nbn * (kD / 128);
-    const int jz = idx / p.n_heads;
-    w.hc = dm::head_coord(idx - jz * p.n_heads, p.h0, p.hcount, p.H, p.Hk);
+    const int jz = (int)dm::fdiv((uint32_t)idx, p.fd_heads);
+    w.hc = dm::head_coord(idx - jz * p.n_heads, p.h0, p.fd_hcount, p.H, p.Hk, p.fd_rep);
     w.bhl = w.hc.b * p.hcount + (w.hc.h - p.h0);
-    w.zh = jz / nbn;                              // d half whose dK / dV columns the item keeps (always 0 at head_dim 128)
+    w.zh = kD == 128 ? 0 : (int)dm::fdiv((uint32_t)jz, p.fd_nbn);   // d half whose dK / dV columns the item keeps
     w.J = jz - w.zh * nbn;
     // m-blocks are counted in the local rows; global position grows with the local index, and both chunks of a row map
     // start on a 128-row pair, so local and global m-block parity agree.  Causal: start at the first local m-block that is
@@ -731,7 +732,8 @@ extern "C" int dm_bwd_fp8_pass1_cp(const void* q8, const void* k8, const void* v
     if (!status) return DM_ERR_CUDA;
     Bwd1Params p{q8s, k8s, v8s, do8s, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), static_cast<uint8_t*>(ds8_ws), psi_ws,
                  sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status, dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, out_fp32,
-                 sh.B * hcount};
+                 sh.B * hcount, dm::make_fastdiv(sh.B * hcount), dm::make_fastdiv(hcount), dm::make_fastdiv(sh.H / sh.Hk),
+                 dm::make_fastdiv(sh.N / 128)};
     // persistent: one CTA per SM walks the (key block, head[, d half]) items, heaviest first
     if ((rc = dmh::prepare_bwd1(err, errlen))) return rc;
     const int smem = (int)(sh.D == 128 ? sizeof(Bwd1Smem<128>) : sizeof(Bwd1Smem<256>)) + 1024;

@@ -54,6 +54,7 @@ struct FwdParams {
     int* status;
     dm::RowMap rm;
     int n_heads;                      // B * hcount: work items are (head, row block), heaviest row blocks first
+    dm::FastDiv fd_heads, fd_hcount, fd_rep;   // divisions by n_heads, hcount and H / Hk
 };
 
 // One work item of a persistent CTA.  Items are numbered rank-major (rank 0 = the row blocks with the most key tiles, all
@@ -70,8 +71,8 @@ __device__ __forceinline__ FwdItem fwd_item(const FwdParams& p, int round) {
     const int nq_blk = p.rm.nq / 128;
     const int idx = round * G + ((round & 1) ? G - 1 - c : c);
     w.valid = idx < p.n_heads * nq_blk;
-    const int rank = idx / p.n_heads;
-    w.hc = dm::head_coord(idx - rank * p.n_heads, p.h0, p.hcount, p.H, p.Hk);
+    const int rank = (int)dm::fdiv((uint32_t)idx, p.fd_heads);
+    w.hc = dm::head_coord(idx - rank * p.n_heads, p.h0, p.fd_hcount, p.H, p.Hk, p.fd_rep);
     w.li = nq_blk - 1 - rank;
     w.I = dm::global_block(p.rm, w.li);
     w.n_tiles = p.causal ? w.I + 1 : p.N / 128;
@@ -314,23 +315,25 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             dm::tc_fence_before();
             dm::mbar_arrive_warp(&s.bar_s_free[b]);            // this S buffer may be overwritten
 
-            const float dsc = q8sc * ks;
-            float gm = -INFINITY;
+            // The group maximum is taken on the raw products: the group's scale is positive, so scaling the maximum gives the
+            // maximum of the scaled scores bit for bit, and the scores themselves are scaled inside the exponent's one
+            // multiply-add below (x = raw * (dsc * log2 e) - ms).  The scale is kept a normal number (it underflows only when a Q
+            // block and a K group are both all zero, where every product is zero anyway), so that a masked -inf stays -inf.
+            const float dsc = fmaxf(q8sc * ks, 1.2e-38f);
             if (p.causal && j == I) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    sv[c] = (g * 64 + c > row) ? -INFINITY : sv[c] * dsc;
-                    gm = fmaxf(gm, sv[c]);
-                }
-            } else {
-                float gm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                for (int c = 0; c < 64; ++c)
+                    if (g * 64 + c > row) sv[c] = -INFINITY;
+            }
+            float gm;
+            {
+                float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]);
 #pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    dm::mul2(sv[c], sv[c + 1], sv[c], sv[c + 1], dsc, dsc);
-                    gm4[c & 3] = fmaxf(gm4[c & 3], sv[c]);
-                    gm4[(c + 1) & 3] = fmaxf(gm4[(c + 1) & 3], sv[c + 1]);
+                for (int c = 4; c < 64; c += 4) {
+                    m0 = dm::fmax3(m0, sv[c], sv[c + 1]);
+                    m1 = dm::fmax3(m1, sv[c + 2], sv[c + 3]);
                 }
-                gm = fmaxf(fmaxf(gm4[0], gm4[1]), fmaxf(gm4[2], gm4[3]));
+                gm = fmaxf(m0, m1) * dsc;
             }
             s.gmax[b][g][row] = gm;
             dm::named_bar_sync(1, kSoftmaxThreads);
@@ -345,18 +348,20 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             // of the product buffers came before the products of tile it - 2, which S of this tile waited for
             s.wgt[rg][g][row] = vs * sigma;
             if (g == 0) s.alpha[rg][row] = alpha;
-            float part = 0.f;
+            float part0 = 0.f, part1 = 0.f;
             uint32_t codes[16];
-            const float nms = -ms;
+            const float nms = -ms, cl = __fmul_rn(dsc, dm::kLog2e);
 #pragma unroll
             for (int c = 0; c < 64; c += 4) {
                 float x0, x1, x2, x3;
-                dm::fma2(x0, x1, sv[c], sv[c + 1], dm::kLog2e, nms, nms);
-                dm::fma2(x2, x3, sv[c + 2], sv[c + 3], dm::kLog2e, nms, nms);
+                dm::fma2(x0, x1, sv[c], sv[c + 1], cl, nms, nms);
+                dm::fma2(x2, x3, sv[c + 2], sv[c + 3], cl, nms, nms);
                 const float p0 = dm::ex2(x0), p1 = dm::ex2(x1), p2 = dm::ex2(x2), p3 = dm::ex2(x3);
-                part += (p0 + p1) + (p2 + p3);
+                dm::add2(part0, part1, p0, p1);
+                dm::add2(part0, part1, p2, p3);
                 codes[c >> 2] = dm::cvt_e4m3x4(p0, p1, p2, p3);
             }
+            const float part = part0 + part1;
             l_part = fmaf(l_part, alpha, sigma * part);
 #pragma unroll
             for (int c = 0; c < 4; ++c)
@@ -466,7 +471,8 @@ extern "C" int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, con
     int* status = dmh::device_status_word(err, errlen);
     if (!status) return DM_ERR_CUDA;
     FwdParams p{q8s, k8s, v8s, static_cast<__nv_bfloat16*>(o), lse, sh.H, sh.Hk, sh.N, h0, hcount, sh.causal, status,
-                dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, sh.B * hcount};
+                dm::RowMap{cp.nq, cp.half_blocks, cp.off0, cp.off1}, sh.B * hcount, dm::make_fastdiv(sh.B * hcount), dm::make_fastdiv(hcount),
+                dm::make_fastdiv(sh.H / sh.Hk)};
     if ((rc = dmh::prepare_fwd(err, errlen))) return rc;
     const int smem = (int)sizeof(FwdSmem) + 1024;
     int sms = 0;

@@ -265,6 +265,17 @@ __device__ __forceinline__ void mul2(float& y0, float& y1, float x0, float x1, f
     y0 = r.x;
     y1 = r.y;
 }
+__device__ __forceinline__ void add2(float& y0, float& y1, float x0, float x1) {
+    const float2 r = __fadd2_rn(make_float2(y0, y1), make_float2(x0, x1));
+    y0 = r.x;
+    y1 = r.y;
+}
+// max of three in one instruction
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // two fp32 -> two e4m3 (round-to-nearest-even, saturate-to-finite), lo in bits 0..7
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     uint16_t r;
