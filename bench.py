@@ -368,9 +368,9 @@ def main():
         total_ms = burst_ms
         for _ in range(repeats - 1):
             total_ms += max_over_ranks(timed_steps(run_step, args.steps))
-    timed = args.steps * repeats
-    n_launch = launches["n"] if graph is None else launches_per_step * timed
-    ms_step = total_ms / timed
+    n_timed = args.steps * repeats
+    n_launch = launches["n"] if graph is None else launches_per_step * n_timed
+    ms_step = total_ms / n_timed
     value = world * flops / (ms_step * 1e-3) / 1e12       # every rank does `flops` (its whole config, or its equal shard)
     burst = {"value": world * flops / (burst_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": burst_ms / args.steps,
              "steps": args.steps}
@@ -514,7 +514,7 @@ def main():
         line = {"metric": "fp8_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong" if cp_mode else scaling, "vs_baseline": None,
-                "timed_steps": timed, "timed_seconds": total_ms * 1e-3, "burst": burst, "eager_ms_per_step": eager_ms,
+                "timed_steps": n_timed, "timed_seconds": total_ms * 1e-3, "burst": burst, "eager_ms_per_step": eager_ms,
                 "dtype": "e4m3", "data": "synthetic",
                 "config": workload_config(args.config, CONFIGS[args.config]),
                 "parallelism": (f"cp{world}: sequence split in zig-zag chunks, K / V codes round an NCCL ring, dK / dV partials to the "

@@ -143,19 +143,31 @@ def local_forward(q, K8, K8s, V8, V8s, cp, B, H, Hk, causal):
     return o, lse, Q8, Q8s
 
 
-def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched):
-    """dq (B, nq, H, D) bf16 and this rank's fp32 partial dK, dV (B, N, Hk, D) over its local rows."""
+def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_pass1=None):
+    """dq (B, nq, H, D) bf16 and this rank's fp32 partial dK, dV (B, N, Hk, D) over its local rows.
+
+    `after_pass1(dkp, dvp)`, if given, is called as soon as pass 1 has been enqueued, with the per-query-head partials
+    (B, N, H, D) fp32, and its result is returned in place of (dkp, dvp): the caller moves the partials to their owners on
+    another stream while pass 2, which needs none of it, runs on this one."""
     dO8, dO8s, delta = _lib.quant_do(dO, None if matched else o)
     if matched:
         delta = _lib.delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, cp=cp)
     dkp, dvp, ws = _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, cp=cp, out_fp32=True)
     N, D = K8.shape[1], K8.shape[2]
+    handed = after_pass1(dkp, dvp) if after_pass1 is not None else None
     dq = _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal, cp=cp)
     del ws
+    if after_pass1 is not None:
+        return dq, handed
+    return (dq,) + fold_query_heads(dkp, dvp, B, N, H, Hk, D)
+
+
+def fold_query_heads(dkp, dvp, B, N, H, Hk, D):
+    """(B, N, H, D) fp32 partials per query head -> (B, N, Hk, D): the sum over the query heads of a KV group, in head order."""
     if H != Hk:
         dkp = _lib.fold_f32(dkp.view(B, N, Hk, H // Hk, D), 3)
         dvp = _lib.fold_f32(dvp.view(B, N, Hk, H // Hk, D), 3)
-    return dq, dkp, dvp
+    return dkp, dvp
 
 
 def owner_slices(x, world: int):
@@ -166,6 +178,17 @@ def owner_slices(x, world: int):
     first = v[:, :world]                                  # chunks 0 .. W-1 belong to ranks 0 .. W-1
     second = v[:, world:].flip(1)                         # chunks 2W-1 .. W belong to ranks 0 .. W-1
     return torch.cat([first, second], dim=2).transpose(0, 1).contiguous()
+
+
+_SIDE = {}
+
+
+def _side_stream(device):
+    """One extra stream per device for the owner exchange of the backward."""
+    key = (device.type, device.index)
+    if key not in _SIDE:
+        _SIDE[key] = torch.cuda.Stream(device)
+    return _SIDE[key]
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -199,12 +222,32 @@ class _DMAttnCP(torch.autograd.Function):
     def backward(ctx, dO):
         o, lse, Q8, Q8s, K8, K8s, V8, V8s = ctx.saved_tensors
         cp, B, H, Hk, causal, matched, group, world = ctx.meta
-        dq, dkp, dvp = local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched)
-        # 4. partials go to the ranks that own the keys and are summed there in rank order
-        both = torch.stack([owner_slices(dkp, world), owner_slices(dvp, world)], dim=1)     # [W, 2, B, 2c, Hk, D]
-        del dkp, dvp
-        mine = exchange_to_owners(both, group)
-        dkv = _lib.fold_f32(mine, 0, torch.bfloat16)                                       # [2, B, 2c, Hk, D]
+        N, D = K8.shape[1], K8.shape[2]
+        main = torch.cuda.current_stream(dO.device) if dO.is_cuda else None
+        side = _side_stream(dO.device) if dO.is_cuda else None
+
+        def to_owners(dkp, dvp):
+            # 4. partials go to the ranks that own the keys and are summed there in rank order.  On GPUs this runs on a second
+            # stream, behind pass 1 and beside pass 2 (which only needs the dS' tiles): the exchange and its folds are about as
+            # long as pass 2 at the long-sequence configuration.
+            def work():
+                fk, fv = fold_query_heads(dkp, dvp, B, N, H, Hk, D)
+                both = torch.stack([owner_slices(fk, world), owner_slices(fv, world)], dim=1)     # [W, 2, B, 2c, Hk, D]
+                mine = exchange_to_owners(both, group)
+                return _lib.fold_f32(mine, 0, torch.bfloat16)                                  # [2, B, 2c, Hk, D]
+            if side is None:
+                return work()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                out = work()
+            for t in (dkp, dvp):
+                t.record_stream(side)
+            return out
+
+        dq, dkv = local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_pass1=to_owners)
+        if side is not None:
+            main.wait_stream(side)
+            dkv.record_stream(main)
         return dq, dkv[0], dkv[1], None, None, None
 
 

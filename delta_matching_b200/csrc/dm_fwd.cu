@@ -37,9 +37,10 @@ struct FwdSmem {
     float gmax[2][2][128];            // [tile parity][key group][row]
     float wgt[kRing][2][128];         // [tile % kRing][key group][row]
     float alpha[kRing][128];
-    float lsum[2][2][128];            // [work item parity][key group][row]
+    float lsum[4][2][128];            // [work item % 4][key group][row]: with one-tile items the softmax warps can be three
+                                      // items ahead of the fold warps
     uint64_t bar_q[2], bar_q_free[2], bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2],
-        bar_d_full[2], bar_d_free, bar_l[2];
+        bar_d_full[2], bar_d_free, bar_l[4];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -103,9 +104,9 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             dm::mbar_init(&s.bar_d_full[i], 1);
             dm::mbar_init(&s.bar_q[i], 1);
             dm::mbar_init(&s.bar_q_free[i], 1);
-            dm::mbar_init(&s.bar_l[i], 8);
         }
         dm::mbar_init(&s.bar_d_free, 4);
+        for (int i = 0; i < 4; ++i) dm::mbar_init(&s.bar_l[i], 8);
         dm::fence_mbar_init();
         dm::tma_prefetch_desc(&tm_q);
         dm::tma_prefetch_desc(&tm_k);
@@ -253,8 +254,8 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             gt += w.n_tiles;
             // ---- the item's epilogue: the softmax warps have left both halves of the denominator
-            dm::mbar_wait(&s.bar_l[r & 1], (r >> 1) & 1, wc);
-            const float l = s.lsum[r & 1][0][row] + s.lsum[r & 1][1][row];
+            dm::mbar_wait(&s.bar_l[r & 3], (r >> 2) & 1, wc);
+            const float l = s.lsum[r & 3][0][row] + s.lsum[r & 3][1][row];
             const bool dead = (l == 0.f) || (l != l);
             const float inv = dead ? 0.f : 1.0f / l;
             const int n_glob = w.li * 128 + row;          // row inside the (local) Q-side tensors
@@ -374,11 +375,11 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
         gt += n_tiles;
         // ---- the item's epilogue: denominator halves to the fold warps, LSE
-        s.lsum[r & 1][g][row] = l_part;
-        dm::mbar_arrive_warp(&s.bar_l[r & 1]);
+        s.lsum[r & 3][g][row] = l_part;
+        dm::mbar_arrive_warp(&s.bar_l[r & 3]);
         dm::named_bar_sync(1, kSoftmaxThreads);
         if (g == 0) {
-            const float l = s.lsum[r & 1][0][row] + s.lsum[r & 1][1][row];
+            const float l = s.lsum[r & 3][0][row] + s.lsum[r & 3][1][row];
             const bool dead = (l == 0.f) || (l != l);
             p.lse[(int64_t)w.hc.bh * p.rm.nq + w.li * 128 + row] = dead ? -INFINITY : m_run + logf(l);
         }

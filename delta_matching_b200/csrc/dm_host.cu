@@ -1,13 +1,33 @@
 // Host-side plumbing of libdm_b200: pointer checks, TMA tensor maps, the per-device status word, build identity.
 #include <stdarg.h>
+#include <atomic>
 #include <mutex>
 
 #include "dm_host.h"
 
 namespace dmh {
 
+// Pointers that have been verified once are remembered by the 2 MiB segment of the address space they lie in (with the device
+// that owns them): CUDA reserves device address ranges in units of at least that size and never hands parts of them to host
+// allocations, so a later pointer in the same segment needs no driver query.  Eight to fourteen queries per entry point were
+// most of the host time of the small kernels.  A direct-mapped table of atomics: a stale or colliding entry only costs a query.
+static std::atomic<uint64_t> g_seg_cache[512];
+
+static bool seg_cached(const void* p, int dev) {
+    const uint64_t seg = reinterpret_cast<uintptr_t>(p) >> 21;
+    const uint64_t want = (seg << 8) | (uint64_t)(dev + 1);
+    return g_seg_cache[(seg ^ (seg >> 9)) & 511].load(std::memory_order_relaxed) == want;
+}
+static void seg_remember(const void* p, int dev) {
+    const uint64_t seg = reinterpret_cast<uintptr_t>(p) >> 21;
+    g_seg_cache[(seg ^ (seg >> 9)) & 511].store((seg << 8) | (uint64_t)(dev + 1), std::memory_order_relaxed);
+}
+
 int check_device_ptr(const void* p, const char* name, char* err, size_t errlen) {
     DM_REQUIRE(p != nullptr, DM_ERR_ARG, "%s is NULL", name);
+    int dev = -1;
+    DM_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 255 && seg_cached(p, dev)) return DM_OK;
     cudaPointerAttributes a;
     cudaError_t e = cudaPointerGetAttributes(&a, p);
     if (e != cudaSuccess) {
@@ -16,10 +36,9 @@ int check_device_ptr(const void* p, const char* name, char* err, size_t errlen) 
     }
     DM_REQUIRE(a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged, DM_ERR_ARG,
                "%s must be CUDA device memory (got a host pointer)", name);
-    int dev = -1;
-    DM_CUDA(cudaGetDevice(&dev));
     DM_REQUIRE(a.type == cudaMemoryTypeManaged || a.device == dev, DM_ERR_ARG,
                "%s lives on device %d but the current device is %d: every tensor must be on the same device", name, a.device, dev);
+    if (a.type == cudaMemoryTypeDevice && dev >= 0 && dev < 255) seg_remember(p, dev);
     return DM_OK;
 }
 
