@@ -9,11 +9,12 @@
 // Key tiles of 128 keys (two 64-key groups) are visited from the diagonal tile downwards.  Per tile:
 //   S = Q K^T            4 x tcgen05.mma (M128 N128 K32) into one of two tensor-memory buffers, up to two tiles ahead
 //   softmax              group max, running max exchanged through shared memory, basis
-//                        ms_g = max(gm_g*l2, m*l2 - 12) - log2(448), codes = e4m3(2^(S*l2 - ms_g)) written to one of two
-//                        swizzled K-major tiles; the denominator is summed from the unrounded p; the tile's alpha and the
-//                        two weights w_g = v8sc_g * 2^(ms_g - m*l2) per row go to a small ring for the fold warps
-//   D_g = C_g V_g        2 x tcgen05.mma per group into zero-initialised tensor-memory temporaries, issued when the codes
-//                        are in shared memory and the previous products have been read
+//                        ms_g = max(gm_g*l2, m*l2 - 12) - log2(448), codes = e4m3(2^(S*l2 - ms_g)) written back into tensor
+//                        memory over the scores they came from (four codes per column, lane = row); the denominator is
+//                        summed from the unrounded p; the tile's alpha and the two weights w_g = v8sc_g * 2^(ms_g - m*l2)
+//                        per row go to a small ring for the fold warps
+//   D_g = C_g V_g        2 x tcgen05.mma per group (A = the codes in tensor memory, B = the V tile) into zero-initialised
+//                        tensor-memory temporaries, issued when the codes are stored and the previous products have been read
 //   O = O * alpha + D_0 w_0 + D_1 w_1   by the fold warps, in that order, while the softmax warps are on the next tile
 // K / V tiles arrive by TMA into a 3-stage ring.  The kernel is persistent: one CTA per SM walks a list of (head, row
 // block) items, and since every role keeps its own place in the list, the loads and S of the next item start while the
@@ -33,7 +34,6 @@ struct FwdSmem {
     alignas(1024) uint8_t q[2][kTile];             // by work item parity: the next item's Q arrives under this item's tail
     alignas(1024) uint8_t k[kStages][kTile];
     alignas(1024) uint8_t v[kStages][kTile];
-    alignas(1024) uint8_t p[2][kTile];
     float gmax[2][2][128];            // [tile parity][key group][row]
     float wgt[kRing][2][128];         // [tile % kRing][key group][row]
     float alpha[kRing][128];
@@ -162,7 +162,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             // ---- D_g = C_g V_g for both key groups once the codes of tile t are in shared memory and the fold warps
             // have read the products of tile t - 1
             constexpr uint32_t idesc_pv = dm::idesc_e4m3(128, 128, false, true);
-            const uint32_t p_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.p[0])), v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
+            const uint32_t v_lo = dm::smem_desc_lo_sw128(dm::smem_u32(s.v[0]));
             int gt = 0;
             for (int r = 0;; ++r) {
                 const FwdItem w = fwd_item(p, r);
@@ -173,13 +173,13 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     dm::mbar_wait(&s.bar_codes[b], (t >> 1) & 1, wc);
                     if (t >= 1) dm::mbar_wait(&s.bar_d_free, (t - 1) & 1, wc);
                     dm::tc_fence_after();
-                    const uint32_t pa = p_lo + b * kSub, va = v_lo + st * kSub;
+                    const uint32_t pa = tmem + b * 128, va = v_lo + st * kSub;     // codes of group g: columns [64 g, 64 g + 16) of S buffer b
                     if (leader) {
                         // group gg: codes columns [64 gg, 64 gg + 64) (K-major, +4 per 64 bytes), V rows [64 gg, +64) (MN-major, +512)
-                        dm::umma_e4m3_lo<false>(t_d0, pa, va, idesc_pv);
-                        dm::umma_e4m3_lo<true>(t_d0, pa + 2, va + 256, idesc_pv);
-                        dm::umma_e4m3_lo<false>(t_d1, pa + 4, va + 512, idesc_pv);
-                        dm::umma_e4m3_lo<true>(t_d1, pa + 6, va + 768, idesc_pv);
+                        dm::umma_e4m3_ts<false>(t_d0, pa, va, idesc_pv);
+                        dm::umma_e4m3_ts<true>(t_d0, pa + 8, va + 256, idesc_pv);
+                        dm::umma_e4m3_ts<false>(t_d1, pa + 64, va + 512, idesc_pv);
+                        dm::umma_e4m3_ts<true>(t_d1, pa + 72, va + 768, idesc_pv);
                         dm::umma_commit(&s.bar_d_full[b]);
                         dm::umma_commit(&s.bar_kv_free[st]);       // K was read by S long ago, V just now
                     }
@@ -364,12 +364,12 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             const float part = part0 + part1;
             l_part = fmaf(l_part, alpha, sigma * part);
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4*>(s.p[b] + dm::sw128(row, g * 64 + c * 16)) =
-                    make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
+            // the codes go back into tensor memory, over the first 16 columns of this thread's own 64 scores (all read by
+            // now): the P V products take them from there as their A operand, four e4m3 per column, lane = row
+            dm::tmem_st16(dm::tmem_addr(tmem + b * 128, lane_base, g * 64), codes);
             m_run = m_new;
-            dm::fence_proxy_async_smem();
+            dm::tmem_st_wait();
+            dm::tc_fence_before();
             dm::mbar_arrive_warp(&s.bar_codes[b]);
         }
 
