@@ -303,9 +303,32 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    def timed_steps(fn, n):
+        """n steps, each bracketed by its own pair of events (the L2 flush between steps stays outside them); the host does
+        not wait for a step before it enqueues the next, so the events measure the device, not the launch path."""
+        evs = []
+        for _ in range(n):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        sync_all()
+        return sum(a.elapsed_time(b) for a, b in evs)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for _ in range(args.warmup):
         step()
     sync_all()
+    # the same step launched from Python (no graph), timed before the capture: what a caller of the API sees
+    eager_ms = None if args.profile else max_over_ranks(timed_steps(step, args.steps)) / args.steps
     # The step (forward + backward through autograd) is captured once into a CUDA graph and replayed: at the small
     # configurations the host's launch path (~0.3 ms of Python per step) is as long as the kernels themselves.  Kernels
     # are counted during the capture.  --no-graph, a sequence split (NCCL inside the step) or a failed capture fall back to
@@ -334,27 +357,6 @@ def main():
     sync_all()
     launches["n"] = 0
 
-    def timed_steps(fn, n):
-        """n steps, each bracketed by its own pair of events (the L2 flush between steps stays outside them); the host does
-        not wait for a step before it enqueues the next, so the events measure the device, not the launch path."""
-        evs = []
-        for _ in range(n):
-            flush.fill_(1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            evs.append((e0, e1))
-        sync_all()
-        return sum(a.elapsed_time(b) for a, b in evs)
-
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     # The timed region: the K steps, repeated (same K steps again) until at least --min-seconds of GPU time have been timed, so
     # that the number is a sustained one and the clock sampler sees the GPU under load.  The first K steps alone are kept as
     # the burst figure.  Every rank runs the same number of repeats (agreed from rank 0's burst time).
@@ -374,8 +376,6 @@ def main():
     value = world * flops / (ms_step * 1e-3) / 1e12       # every rank does `flops` (its whole config, or its equal shard)
     burst = {"value": world * flops / (burst_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": burst_ms / args.steps,
              "steps": args.steps}
-    # the same step launched from Python (no graph): what a caller of the API sees at small shapes
-    eager_ms = ms_step if graph is None else max_over_ranks(timed_steps(step, args.steps)) / args.steps
     status = _lib.device_status(local)
     if status != 0:
         raise SystemExit(f"bench: a kernel reported a bounded-wait timeout (device status {status}); the timed numbers are void")

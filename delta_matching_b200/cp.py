@@ -143,21 +143,44 @@ def local_forward(q, K8, K8s, V8, V8s, cp, B, H, Hk, causal):
     return o, lse, Q8, Q8s
 
 
-def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_pass1=None):
-    """dq (B, nq, H, D) bf16 and this rank's fp32 partial dK, dV (B, N, Hk, D) over its local rows.
+def heads_per_call(B, H, Hk, nq, N, limit_bytes=None):
+    """Query heads per pass-1 / pass-2 call of a rank: whole KV groups, as many as keep the dS' tiles (B * heads * nq * N
+    bytes) inside the workspace limit of the head-group split (DM_BWD_WS_LIMIT_GB, 8 GiB by default), and a divisor of H."""
+    from . import split
+    limit = split._BWD_WS_LIMIT if limit_bytes is None else limit_bytes
+    rep = H // Hk
+    best = rep
+    for groups in range(1, Hk + 1):
+        if Hk % groups == 0 and B * groups * rep * nq * N <= limit:
+            best = groups * rep
+    return best
 
-    `after_pass1(dkp, dvp)`, if given, is called as soon as pass 1 has been enqueued, with the per-query-head partials
-    (B, N, H, D) fp32, and its result is returned in place of (dkp, dvp): the caller moves the partials to their owners on
-    another stream while pass 2, which needs none of it, runs on this one."""
+
+def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_group=None):
+    """dq (B, nq, H, D) bf16 and this rank's fp32 partial dK, dV (B, N, Hk, D) over its local rows.  Pass 1 and pass 2 run
+    per group of KV groups (heads_per_call), so the dS' workspace stays bounded at long sequences.
+
+    `after_group(dkp, dvp, h0, hcount)`, if given, is called as soon as a group's pass 1 has been enqueued, with views of the
+    per-query-head partials (B, N, hcount, D) fp32 of that group; the list of its results is returned in place of the folded
+    partials: the caller moves every group's partials to their owners on another stream while the other passes run."""
     dO8, dO8s, delta = _lib.quant_do(dO, None if matched else o)
     if matched:
         delta = _lib.delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, cp=cp)
-    dkp, dvp, ws = _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, cp=cp, out_fp32=True)
-    N, D = K8.shape[1], K8.shape[2]
-    handed = after_pass1(dkp, dvp) if after_pass1 is not None else None
-    dq = _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal, cp=cp)
+    N, D, nq = K8.shape[1], K8.shape[2], Q8.shape[1]
+    hp = heads_per_call(B, H, Hk, nq, N)
+    dev = Q8.device
+    dkp = torch.empty(B, N, H, D, device=dev, dtype=torch.float32)
+    dvp = torch.empty(B, N, H, D, device=dev, dtype=torch.float32)
+    dq = torch.empty(B, nq, H, D, device=dev, dtype=torch.bfloat16)
+    ws, handed = None, []
+    for h0 in range(0, H, hp):
+        _, _, ws = _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, h0=h0, hcount=hp, out=(dkp, dvp),
+                                  ws=ws, cp=cp, out_fp32=True)
+        if after_group is not None:
+            handed.append(after_group(dkp[:, :, h0:h0 + hp], dvp[:, :, h0:h0 + hp], h0, hp))
+        _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal, h0=h0, hcount=hp, out=dq, cp=cp)
     del ws
-    if after_pass1 is not None:
+    if after_group is not None:
         return dq, handed
     return (dq,) + fold_query_heads(dkp, dvp, B, N, H, Hk, D)
 
@@ -223,18 +246,18 @@ class _DMAttnCP(torch.autograd.Function):
         o, lse, Q8, Q8s, K8, K8s, V8, V8s = ctx.saved_tensors
         cp, B, H, Hk, causal, matched, group, world = ctx.meta
         N, D = K8.shape[1], K8.shape[2]
+        rep = H // Hk
         main = torch.cuda.current_stream(dO.device) if dO.is_cuda else None
         side = _side_stream(dO.device) if dO.is_cuda else None
 
-        def to_owners(dkp, dvp):
-            # 4. partials go to the ranks that own the keys and are summed there in rank order.  On GPUs this runs on a second
-            # stream, behind pass 1 and beside pass 2 (which only needs the dS' tiles): the exchange and its folds are about as
-            # long as pass 2 at the long-sequence configuration.
+        def to_owners(dkp, dvp, h0, hcount):
+            # 4. a group's partials go to the ranks that own the keys and are summed there in rank order.  On GPUs this runs on
+            # a second stream, behind the group's pass 1 and beside its pass 2 and the next group's passes.
             def work():
-                fk, fv = fold_query_heads(dkp, dvp, B, N, H, Hk, D)
-                both = torch.stack([owner_slices(fk, world), owner_slices(fv, world)], dim=1)     # [W, 2, B, 2c, Hk, D]
+                fk, fv = fold_query_heads(dkp.contiguous(), dvp.contiguous(), B, N, hcount, hcount // rep, D)
+                both = torch.stack([owner_slices(fk, world), owner_slices(fv, world)], dim=1)     # [W, 2, B, 2c, groups, D]
                 mine = exchange_to_owners(both, group)
-                return _lib.fold_f32(mine, 0, torch.bfloat16)                                  # [2, B, 2c, Hk, D]
+                return _lib.fold_f32(mine, 0, torch.bfloat16)                                  # [2, B, 2c, groups, D]
             if side is None:
                 return work()
             side.wait_stream(main)
@@ -244,10 +267,13 @@ class _DMAttnCP(torch.autograd.Function):
                 t.record_stream(side)
             return out
 
-        dq, dkv = local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_pass1=to_owners)
+        dq, parts = local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_group=to_owners)
         if side is not None:
             main.wait_stream(side)
-            dkv.record_stream(main)
+        dkv = parts[0] if len(parts) == 1 else torch.cat(parts, dim=3)
+        if side is not None:
+            for t in parts:
+                t.record_stream(main)
         return dq, dkv[0], dkv[1], None, None, None
 
 
