@@ -60,6 +60,7 @@ _SIGNATURES = {
     "dm_kmean_partials": (C.c_int, [_P, DmStrides, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_kmean_fold": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_fold_f32": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int64, C.c_int32, _P, _P, *_ERR]),
+    "dm_fold_to_owners": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_fwd_fp8_cp": (C.c_int, [_P] * 6 + [DmShape, DmCp, C.c_int32, C.c_int32, _P, _P, _P, *_ERR]),
     "dm_delta_fp8_cp": (C.c_int, [_P] * 9 + [DmShape, DmCp, C.c_int32, C.c_int32, _P, _P, *_ERR]),
     "dm_bwd_workspace_bytes_cp": (C.c_int, [DmShape, DmCp, C.c_int32, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
@@ -332,6 +333,17 @@ def fold_f32(x, count_dim, out_dtype=torch.float32):
         out = torch.empty(shape[:count_dim] + shape[count_dim + 1:], device=x.device, dtype=out_dtype)
         _call("dm_fold_f32", _ptr(x), outer, shape[count_dim], inner, 1 if out_dtype == torch.bfloat16 else 0, _ptr(out),
               _stream(x.device))
+    return out
+
+
+def fold_to_owners(dkp, dvp, Hk, world):
+    """fp32 partials (B, N, H, D) of dK and dV over all keys -> [world, 2, B, N / world, Hk, D] fp32: summed over the query
+    heads of each KV group in head order, slice d holding the rows rank d owns under the zig-zag split."""
+    assert dkp.dtype == torch.float32 and dkp.is_contiguous() and dvp.is_contiguous() and dkp.shape == dvp.shape
+    B, N, H, D = dkp.shape
+    with torch.cuda.device(dkp.device):
+        out = torch.empty(world, 2, B, N // world, Hk, D, device=dkp.device, dtype=torch.float32)
+        _call("dm_fold_to_owners", _ptr(dkp), _ptr(dvp), B, N, H, Hk, D, world, _ptr(out), _stream(dkp.device))
     return out
 
 

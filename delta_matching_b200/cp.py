@@ -156,13 +156,10 @@ def heads_per_call(B, H, Hk, nq, N, limit_bytes=None):
     return best
 
 
-def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_group=None):
-    """dq (B, nq, H, D) bf16 and this rank's fp32 partial dK, dV (B, N, Hk, D) over its local rows.  Pass 1 and pass 2 run
-    per group of KV groups (heads_per_call), so the dS' workspace stays bounded at long sequences.
-
-    `after_group(dkp, dvp, h0, hcount)`, if given, is called as soon as a group's pass 1 has been enqueued, with views of the
-    per-query-head partials (B, N, hcount, D) fp32 of that group; the list of its results is returned in place of the folded
-    partials: the caller moves every group's partials to their owners on another stream while the other passes run."""
+def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, fold=True):
+    """dq (B, nq, H, D) bf16 and this rank's fp32 partial dK, dV over its local rows: (B, N, Hk, D), folded over the query
+    heads of each KV group, or with fold=False the per-query-head partials (B, N, H, D) as pass 1 left them.  Pass 1 and
+    pass 2 run per group of KV groups (heads_per_call), so the dS' workspace stays bounded at long sequences."""
     dO8, dO8s, delta = _lib.quant_do(dO, None if matched else o)
     if matched:
         delta = _lib.delta_fp8(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, B, H, Hk, causal, cp=cp)
@@ -172,16 +169,14 @@ def local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, 
     dkp = torch.empty(B, N, H, D, device=dev, dtype=torch.float32)
     dvp = torch.empty(B, N, H, D, device=dev, dtype=torch.float32)
     dq = torch.empty(B, nq, H, D, device=dev, dtype=torch.bfloat16)
-    ws, handed = None, []
+    ws = None
     for h0 in range(0, H, hp):
         _, _, ws = _lib.bwd_pass1(Q8, K8, V8, dO8, Q8s, K8s, V8s, dO8s, lse, delta, B, H, Hk, causal, h0=h0, hcount=hp, out=(dkp, dvp),
                                   ws=ws, cp=cp, out_fp32=True)
-        if after_group is not None:
-            handed.append(after_group(dkp[:, :, h0:h0 + hp], dvp[:, :, h0:h0 + hp], h0, hp))
         _lib.bwd_pass2(ws, K8, B, H, Hk, N, D, causal, h0=h0, hcount=hp, out=dq, cp=cp)
     del ws
-    if after_group is not None:
-        return dq, handed
+    if not fold:
+        return dq, dkp, dvp
     return (dq,) + fold_query_heads(dkp, dvp, B, N, H, Hk, D)
 
 
@@ -201,17 +196,6 @@ def owner_slices(x, world: int):
     first = v[:, :world]                                  # chunks 0 .. W-1 belong to ranks 0 .. W-1
     second = v[:, world:].flip(1)                         # chunks 2W-1 .. W belong to ranks 0 .. W-1
     return torch.cat([first, second], dim=2).transpose(0, 1).contiguous()
-
-
-_SIDE = {}
-
-
-def _side_stream(device):
-    """One extra stream per device for the owner exchange of the backward."""
-    key = (device.type, device.index)
-    if key not in _SIDE:
-        _SIDE[key] = torch.cuda.Stream(device)
-    return _SIDE[key]
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -245,35 +229,14 @@ class _DMAttnCP(torch.autograd.Function):
     def backward(ctx, dO):
         o, lse, Q8, Q8s, K8, K8s, V8, V8s = ctx.saved_tensors
         cp, B, H, Hk, causal, matched, group, world = ctx.meta
-        N, D = K8.shape[1], K8.shape[2]
-        rep = H // Hk
-        main = torch.cuda.current_stream(dO.device) if dO.is_cuda else None
-        side = _side_stream(dO.device) if dO.is_cuda else None
-
-        def to_owners(dkp, dvp, h0, hcount):
-            # 4. a group's partials go to the ranks that own the keys and are summed there in rank order.  On GPUs this runs on
-            # a second stream, behind the group's pass 1 and beside its pass 2 and the next group's passes.
-            def work():
-                fk, fv = fold_query_heads(dkp.contiguous(), dvp.contiguous(), B, N, hcount, hcount // rep, D)
-                both = torch.stack([owner_slices(fk, world), owner_slices(fv, world)], dim=1)     # [W, 2, B, 2c, groups, D]
-                mine = exchange_to_owners(both, group)
-                return _lib.fold_f32(mine, 0, torch.bfloat16)                                  # [2, B, 2c, groups, D]
-            if side is None:
-                return work()
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                out = work()
-            for t in (dkp, dvp):
-                t.record_stream(side)
-            return out
-
-        dq, parts = local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, after_group=to_owners)
-        if side is not None:
-            main.wait_stream(side)
-        dkv = parts[0] if len(parts) == 1 else torch.cat(parts, dim=3)
-        if side is not None:
-            for t in parts:
-                t.record_stream(main)
+        dq, dkp, dvp = local_backward(dO, o, lse, Q8, Q8s, K8, K8s, V8, V8s, cp, B, H, Hk, causal, matched, fold=False)
+        # 4. the partials are folded over the query heads straight into one slice per owner of the keys, go there in one
+        # exchange after the last pass, and are summed in rank order.  (Exchanging group by group on a second stream beside the
+        # next group's passes was slower: the persistent kernels give every SM a fixed share of the items, so the SMs that an
+        # exchange kernel holds while it waits for its peer finish their share late and the whole launch waits for them.)
+        both = _lib.fold_to_owners(dkp, dvp, Hk, world)                                       # [W, 2, B, 2c, Hk, D]
+        del dkp, dvp
+        dkv = _lib.fold_f32(exchange_to_owners(both, group), 0, torch.bfloat16)               # [2, B, 2c, Hk, D]
         return dq, dkv[0], dkv[1], None, None, None
 
 

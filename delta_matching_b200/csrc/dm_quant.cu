@@ -414,6 +414,59 @@ extern "C" int dm_fold_f32(const float* in, int64_t outer, int32_t count, int64_
     return DM_OK;
 }
 
+// ---- fold over the query heads straight into the owners' layout of a zig-zag sequence split ---------------------------
+// out[d, kv, b, rl, g, :] = sum over j ascending of part_kv[b, key(d, rl), g * rep + j, :], where rank d of W owns the
+// sequence chunks d and 2W-1-d of c = N / 2W keys each: key(d, rl) = d c + rl for rl < c, (2W-1-d) c + rl - c otherwise.
+// Same order of additions as fold_f32_kernel over the query heads; slice d is what this rank sends to rank d.
+namespace {
+__global__ void __launch_bounds__(256) fold_to_owners_kernel(const float4* __restrict__ dkp, const float4* __restrict__ dvp, int B,
+                                                             int N, int Hk, int rep, int d4, int W, float4* __restrict__ out) {
+    const int c = N / (2 * W);
+    const int64_t per_row = (int64_t)Hk * d4;                       // float4 per (kv, b, key) row of the output
+    const int64_t total = (int64_t)W * 2 * B * 2 * c * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t row = i / per_row;
+        const int64_t e = i - row * per_row;                        // g * d4 + i4
+        const int g = (int)(e / d4), i4 = (int)(e - (int64_t)g * d4);
+        const int rl = (int)(row % (2 * c)); row /= 2 * c;
+        const int b = (int)(row % B); row /= B;
+        const int kv = (int)(row & 1), d = (int)(row >> 1);
+        const int key = rl < c ? d * c + rl : (2 * W - 1 - d) * c + (rl - c);
+        const float4* p = (kv ? dvp : dkp) + (((int64_t)b * N + key) * Hk + g) * rep * d4 + i4;
+        float4 a = p[0];
+        for (int j = 1; j < rep; ++j) {
+            const float4 x = p[(int64_t)j * d4];
+            a.x = __fadd_rn(a.x, x.x);
+            a.y = __fadd_rn(a.y, x.y);
+            a.z = __fadd_rn(a.z, x.z);
+            a.w = __fadd_rn(a.w, x.w);
+        }
+        out[i] = a;
+    }
+}
+}  // namespace
+
+extern "C" int dm_fold_to_owners(const float* dkp, const float* dvp, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, int32_t world,
+                                 float* out, void* stream, char* err, size_t errlen) {
+    DM_REQUIRE(B > 0 && N > 0 && Hk > 0 && H > 0 && H % Hk == 0 && D > 0 && D % 4 == 0 && world > 0 && N % (2 * world) == 0, DM_ERR_ARG,
+               "dm_fold_to_owners: needs nheads a multiple of nheads_k, head_dim a multiple of 4 and seqlen a multiple of 2 x ranks "
+               "(got B %d N %d H %d Hk %d D %d ranks %d)", B, N, H, Hk, D, world);
+    int rc;
+    if ((rc = dmh::check_device_ptr(dkp, "dkp", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(dvp, "dvp", err, errlen))) return rc;
+    if ((rc = dmh::check_device_ptr(out, "out", err, errlen))) return rc;
+    DM_REQUIRE(dmh::aligned16(dkp) && dmh::aligned16(dvp) && dmh::aligned16(out), DM_ERR_ARG,
+               "dm_fold_to_owners: pointers must be 16-byte aligned");
+    const int64_t total = (int64_t)2 * B * N * Hk * (D / 4);
+    const int64_t want = (total + 255) / 256;
+    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    fold_to_owners_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(dkp), reinterpret_cast<const float4*>(dvp), B, N, Hk, H / Hk, D / 4, world,
+        reinterpret_cast<float4*>(out));
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+
 template <int D, int MODE>
 static void launch_quant(const void* x, DmStrides xs, const void* o, DmStrides os, const float* km, void* codes, float* scales,
                          float* delta, int B, int heads, int N, cudaStream_t st) {

@@ -117,6 +117,13 @@ int dm_kmean_fold(const float* partials, int32_t B, int32_t Hk, int32_t N, int32
 int dm_fold_f32(const float* in, int64_t outer, int32_t count, int64_t inner, int32_t out_is_bf16, void* out, void* stream, char* err,
                 size_t errlen);
 
+/* The same fold over the query heads for a zig-zag sequence split, written straight into the layout of the exchange that
+ * follows: dkp / dvp are this rank's fp32 partials [B, N, H, D] over all keys; out is [ranks, 2 (dK, dV), B, N / ranks,
+ * Hk, D] fp32 whose slice d holds the keys rank d owns (chunk d, then chunk 2 ranks - 1 - d, of N / (2 ranks) keys each).
+ * Same bits as dm_fold_f32 over the heads followed by a gather of the rows.  No counterpart in the reference. */
+int dm_fold_to_owners(const float* dkp, const float* dvp, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, int32_t world,
+                      float* out, void* stream, char* err, size_t errlen);
+
 int dm_fwd_fp8_cp(const void* q8, const void* k8, const void* v8, const float* q8s, const float* k8s, const float* v8s,
                   DmShape s, DmCp cp, int32_t h0, int32_t hcount, void* o_bf16, float* lse, void* stream, char* err, size_t errlen);
 

@@ -66,6 +66,19 @@ def test_fold_f32_ordered_sum():
     assert torch.equal(_lib.fold_f32(x, 1, torch.bfloat16), want.to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("world,H,Hk", [(2, 8, 2), (4, 4, 4), (8, 6, 2)])
+def test_fold_to_owners_is_the_head_fold_then_the_row_gather(world, H, Hk):
+    from delta_matching_b200 import _lib, cp as cpm
+    B, N, D = 2, 64 * world, 128
+    dkp, dvp = torch.randn(B, N, H, D, device="cuda"), torch.randn(B, N, H, D, device="cuda")
+    fk, fv = cpm.fold_query_heads(dkp, dvp, B, N, H, Hk, D)
+    want = torch.stack([cpm.owner_slices(fk, world), cpm.owner_slices(fv, world)], dim=1)
+    got = _lib.fold_to_owners(dkp, dvp, Hk, world)
+    assert got.shape == want.shape and torch.equal(got, want)
+    with pytest.raises(RuntimeError, match="multiple of 2 x ranks"):
+        _lib.fold_to_owners(dkp[:, :N - 1].contiguous(), dvp[:, :N - 1].contiguous(), Hk, world)
+
+
 def test_row_map_is_validated():
     from delta_matching_b200 import _lib
     Q8 = torch.zeros(2, 512, 128, device="cuda").to(_lib.E4M3)
