@@ -96,88 +96,133 @@ __device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16
     constexpr int BLK = (MODE == 1 || MODE == 2) ? (D == 128 ? 64 : 32) : (D == 128 ? 128 : 64);
     constexpr int E = D / 32;             // elements per lane
     constexpr int RPW = BLK / 8;          // rows per warp
+    // Q, V and dO: the block maximum is a maximum of bf16 magnitudes (Q's multiply by a positive constant is monotone, so
+    // it commutes with the maximum), which orders like their bit patterns: two elements per instruction, on the raw pairs.
+    // K subtracts a per-column mean first and takes the float route.
+    constexpr bool kPackedMax = MODE != 1;
     const int b = bh / heads, h = bh % heads;
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     __shared__ float s_amax[8];
+    __shared__ uint32_t s_bits[8];
 
     float kmv[E];
     if (MODE == 1) {
 #pragma unroll
         for (int e = 0; e < E; ++e) kmv[e] = km[(int64_t)bh * D + l * E + e];
     }
-    float v[RPW][E];
-    float amax = 0.f;
+    // the block stays in registers as raw bf16 pairs between the maximum and the codes
+    uint32_t u[RPW][E / 2];
     const __nv_bfloat16* xbase = x + b * sb + h * sh + l * E;
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
         const int row = blk * BLK + r * 8 + w;
         const __nv_bfloat16* p = xbase + (int64_t)row * sn;
-        uint32_t u[E / 2];
         if (E == 4) {
             uint2 t = *reinterpret_cast<const uint2*>(p);
-            u[0] = t.x; u[1] = t.y;
+            u[r][0] = t.x; u[r][1] = t.y;
         } else {
             uint4 t = *reinterpret_cast<const uint4*>(p);
-            u[0] = t.x; u[1] = t.y; u[E / 2 - 2] = t.z; u[E / 2 - 1] = t.w;
-        }
-#pragma unroll
-        for (int e = 0; e < E / 2; ++e) {
-            v[r][2 * e] = bf16_lo(u[e]);
-            v[r][2 * e + 1] = bf16_hi(u[e]);
-        }
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            if (MODE == 0) v[r][e] = __fmul_rn(v[r][e], sm);
-            if (MODE == 1) v[r][e] = __fsub_rn(v[r][e], kmv[e]);
-            amax = fmaxf(amax, fabsf(v[r][e]));
+            u[r][0] = t.x; u[r][1] = t.y; u[r][E / 2 - 2] = t.z; u[r][E / 2 - 1] = t.w;
         }
     }
+    // element e of row r as the float the block is quantized from
+    auto value = [&](int r, int e) -> float {
+        float f = (e & 1) ? bf16_hi(u[r][e >> 1]) : bf16_lo(u[r][e >> 1]);
+        if (MODE == 0) f = __fmul_rn(f, sm);
+        if (MODE == 1) f = __fsub_rn(f, kmv[e]);
+        return f;
+    };
+
+    float amax = 0.f;
+    bool finite = false;                  // every element of the block is finite (known on the packed route only)
+    if (kPackedMax) {
+        uint32_t m = 0;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    if (l == 0) s_amax[w] = amax;
-    __syncthreads();
-    amax = s_amax[0];
+        for (int r = 0; r < RPW; ++r)
 #pragma unroll
-    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_amax[i]);
+            for (int e = 0; e < E / 2; ++e) m = __vmaxu2(m, u[r][e] & 0x7FFF7FFFu);
+        m = max(m & 0xFFFFu, m >> 16);
+        m = __reduce_max_sync(0xffffffffu, m);
+        if (l == 0) s_bits[w] = m;
+        __syncthreads();
+        m = s_bits[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = max(m, s_bits[i]);
+        finite = m < 0x7F80u;
+        amax = __uint_as_float(m << 16);
+        if (MODE == 0) amax = __fmul_rn(amax, sm);
+    }
+    if (!kPackedMax || !finite) {         // uniform over the block.  A NaN is skipped by the maximum, an infinity wins it.
+        amax = 0.f;
+#pragma unroll
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+            for (int e = 0; e < E; ++e) amax = fmaxf(amax, fabsf(value(r, e)));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (l == 0) s_amax[w] = amax;
+        __syncthreads();
+        amax = s_amax[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_amax[i]);
+    }
     const float base = fmaxf(amax, kTiny);
     const float s = (MODE >= 3) ? __fmul_rn(base, __fdiv_rn(1.0f, kE4M3Max)) : __fdiv_rn(base, kE4M3Max);
     if (threadIdx.x == 0) scales[(int64_t)bh * (N / BLK) + blk] = s;
 
     uint8_t* cbase = codes + ((int64_t)bh * N) * D + l * E;
     const float rcp = __frcp_rn(s);
-    auto emit = [&](auto exact_rcp) {
-        constexpr bool kExactRcp = decltype(exact_rcp)::value;
+    // kFinite: all elements finite and the scale inside the reciprocal's range.  Then the quotient is finite, so the
+    // conversion's own saturation is the clamp, and its sign is the element's: the sign bits are copied from the bf16
+    // pairs into the four codes at once instead of a copysign per element.
+    auto emit = [&](auto exact_rcp, auto all_finite) {
+        constexpr bool kExactRcp = decltype(exact_rcp)::value, kFinite = decltype(all_finite)::value;
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
             const int row = blk * BLK + r * 8 + w;
-            float qv[E];
+            uint32_t c4[E / 4];
 #pragma unroll
-            for (int e = 0; e < E; ++e) qv[e] = fminf(fmaxf(quotient_rn<kExactRcp>(v[r][e], s, rcp), -kE4M3Max), kE4M3Max);
+            for (int g = 0; g < E / 4; ++g) {
+                float qv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float xv = value(r, 4 * g + e);
+                    if (kFinite) {
+                        float q = __fmul_rn(xv, rcp);
+                        q = __fmaf_rn(__fmaf_rn(-q, s, xv), rcp, q);
+                        qv[e] = __fmaf_rn(__fmaf_rn(-q, s, xv), rcp, q);
+                    } else {
+                        qv[e] = fminf(fmaxf(quotient_rn<kExactRcp>(xv, s, rcp), -kE4M3Max), kE4M3Max);
+                    }
+                }
+                c4[g] = e4m3x4(qv[0], qv[1], qv[2], qv[3]);
+                if (kFinite) {
+                    const uint32_t sign = __byte_perm(u[r][2 * g], u[r][2 * g + 1], 0x7531);   // the high byte of each bf16
+                    c4[g] = (c4[g] & 0x7F7F7F7Fu) | (sign & 0x80808080u);
+                }
+            }
             if (E == 4) {
-                *reinterpret_cast<uint32_t*>(cbase + (int64_t)row * D) = e4m3x4(qv[0], qv[1], qv[2], qv[3]);
+                *reinterpret_cast<uint32_t*>(cbase + (int64_t)row * D) = c4[0];
             } else {
-                uint2 t;
-                t.x = e4m3x4(qv[0], qv[1], qv[2], qv[3]);
-                t.y = e4m3x4(qv[E - 4], qv[E - 3], qv[E - 2], qv[E - 1]);
-                *reinterpret_cast<uint2*>(cbase + (int64_t)row * D) = t;
+                *reinterpret_cast<uint2*>(cbase + (int64_t)row * D) = make_uint2(c4[0], c4[E / 4 - 1]);
             }
             if (MODE == 4) {
-                // stale delta from the RAW dO (v holds it unscaled in this mode) and the bf16 O
+                // stale delta from the RAW dO and the bf16 O
                 const __nv_bfloat16* po = o + b * ob + h * oh + (int64_t)row * on + l * E;
-                uint32_t u[E / 2];
+                uint32_t uo[E / 2];
                 if (E == 4) {
                     uint2 t = *reinterpret_cast<const uint2*>(po);
-                    u[0] = t.x; u[1] = t.y;
+                    uo[0] = t.x; uo[1] = t.y;
                 } else {
                     uint4 t = *reinterpret_cast<const uint4*>(po);
-                    u[0] = t.x; u[1] = t.y; u[E / 2 - 2] = t.z; u[E / 2 - 1] = t.w;
+                    uo[0] = t.x; uo[1] = t.y; uo[E / 2 - 2] = t.z; uo[E / 2 - 1] = t.w;
                 }
-                float acc = __fmul_rn(v[r][0], bf16_lo(u[0]));
-                acc = __fadd_rn(acc, __fmul_rn(v[r][1], bf16_hi(u[0])));
+                float acc = __fmul_rn(bf16_lo(u[r][0]), bf16_lo(uo[0]));
+                acc = __fadd_rn(acc, __fmul_rn(bf16_hi(u[r][0]), bf16_hi(uo[0])));
 #pragma unroll
                 for (int e = 1; e < E / 2; ++e) {
-                    acc = __fadd_rn(acc, __fmul_rn(v[r][2 * e], bf16_lo(u[e])));
-                    acc = __fadd_rn(acc, __fmul_rn(v[r][2 * e + 1], bf16_hi(u[e])));
+                    acc = __fadd_rn(acc, __fmul_rn(bf16_lo(u[r][e]), bf16_lo(uo[e])));
+                    acc = __fadd_rn(acc, __fmul_rn(bf16_hi(u[r][e]), bf16_hi(uo[e])));
                 }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
@@ -185,8 +230,10 @@ __device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16
             }
         }
     };
-    if (s >= 0x1p-60f && s <= 0x1p60f) emit(std::true_type{});
-    else emit(std::false_type{});
+    const bool in_range = s >= 0x1p-60f && s <= 0x1p60f;
+    if (kPackedMax && finite && in_range) emit(std::true_type{}, std::true_type{});
+    else if (in_range) emit(std::true_type{}, std::false_type{});
+    else emit(std::false_type{}, std::false_type{});
 }
 
 template <int D, int MODE>

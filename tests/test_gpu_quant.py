@@ -74,6 +74,69 @@ def test_expanded_grad_and_saturation():
     assert (gc.float() == 448.0).all()
 
 
+def _special_blocks(rows, D, seed):
+    """One block of `rows` rows per case: signed zeros, bf16 subnormals, a NaN, an infinity, both, all zero, huge, tiny."""
+    g = torch.Generator("cpu").manual_seed(seed)
+    cases = []
+    for kind in range(8):
+        x = torch.randn(rows, D, generator=g)
+        if kind == 0:
+            x[::3] = 0.0
+            x[1::7] = -0.0
+        elif kind == 1:
+            x[::2] = x[::2] * 1e-39                       # bf16 subnormals beside ordinary values
+        elif kind == 2:
+            x[5, 7] = float("nan")
+        elif kind == 3:
+            x[9, 1] = float("inf")
+        elif kind == 4:
+            x[3, 3] = float("-inf")
+            x[4, 4] = float("nan")
+        elif kind == 5:
+            x.zero_()
+            x[::2] = -0.0
+        elif kind == 6:
+            x = x * 1e37
+        else:
+            x = x * 1e-25
+        cases.append(x)
+    return torch.cat(cases).to(torch.bfloat16)
+
+
+def _expected_codes(v, rows, mul_inv):
+    """What the quantizers define for non-finite data: the block maximum skips a NaN and is won by an infinity, and a NaN
+    quotient (a NaN element, or infinity over infinity) becomes the code of -448."""
+    n_blk = v.shape[0] // rows
+    vb = v.view(n_blk, -1)
+    amax = torch.where(vb.isnan(), torch.zeros_like(vb), vb.abs()).amax(dim=1)
+    base = torch.maximum(amax, torch.tensor(1e-30, dtype=torch.float32))
+    s = base * (torch.tensor(1.0) / torch.tensor(448.0)) if mul_inv else base / torch.tensor(448.0)
+    q = vb / s[:, None]
+    q = torch.where(q.isnan(), torch.full_like(q, -448.0), q)
+    return O.to_e4m3(q).view(v.shape), s
+
+
+@pytest.mark.parametrize("D", [128, 256])
+def test_signed_zeros_subnormals_and_non_finite_blocks(D):
+    rq, rkv = (128, 64) if D == 128 else (64, 32)
+    for mode, rows in ((0, rq), (2, rkv), (3, rq)):
+        x = _special_blocks(rows, D, 40 + mode)                       # [8 * rows, D]
+        n = x.shape[0]
+        n_pad = -(-n // 256) * 256                                   # the sequence length the shape check wants
+        x = torch.cat([x, torch.ones(n_pad - n, D, dtype=torch.bfloat16)])
+        v = x.float() * torch.tensor(D ** -0.5, dtype=torch.float32) if mode == 0 else x.float()
+        want_c, want_s = _expected_codes(v, rows, mul_inv=(mode == 3))
+        xd = x.view(1, n_pad, 1, D).cuda()
+        if mode == 3:
+            gc, gs, _ = _lib.quant_do(xd)
+        else:
+            gc, gs = _lib.quant(mode, xd)
+        assert torch.equal(gs.cpu().view(-1), want_s), f"mode {mode}: scales differ"
+        got = gc.cpu().view(torch.uint8).view(n_pad, D)
+        bad = (got != want_c.view(torch.uint8)).nonzero()
+        assert bad.numel() == 0, f"mode {mode}: codes differ first at {bad[0].tolist()} (case {int(bad[0][0]) // rows})"
+
+
 def test_gqa_fold():
     g = torch.Generator("cpu").manual_seed(5)
     x = torch.randn(2, 256, 8, 128, generator=g).to(torch.bfloat16)
