@@ -40,7 +40,7 @@ struct FwdSmem {
     float lsum[4][2][128];            // [work item % 4][key group][row]: with one-tile items the softmax warps can be three
                                       // items ahead of the fold warps
     uint64_t bar_q[2], bar_q_free[2], bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2],
-        bar_d_full[2], bar_d_free, bar_l[4], bar_gm[2][4];
+        bar_d_full[2], bar_d_free, bar_l[4];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -107,7 +107,6 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         dm::mbar_init(&s.bar_d_free, 4);
         for (int i = 0; i < 4; ++i) dm::mbar_init(&s.bar_l[i], 8);
-        for (int i = 0; i < 8; ++i) dm::mbar_init(&s.bar_gm[i >> 2][i & 3], 2);
         dm::fence_mbar_init();
         dm::tma_prefetch_desc(&tm_q);
         dm::tma_prefetch_desc(&tm_k);
@@ -299,11 +298,6 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
         float ks_n = ks_nx, vs_n = vs_nx;
         first_scales(fwd_item(p, r + 1));
-        // The group maximum of tile it + 1 is taken one tile early, under the last exponentials of tile it (which keep the
-        // MUFU busy and leave issue slots free), if its S has arrived by then: the tile's own chain then starts at the
-        // exchange of the two groups' maxima.  The diagonal tile is an item's first, so a tile read early is never masked.
-        float gm_pre = 0.f;
-        bool have_pre = false;
         for (int it = 0; it < n_tiles; ++it) {
             const int t = gt + it, j = n_tiles - 1 - it, b = t & 1, rg = t % kRing;
             const float ks = ks_n, vs = vs_n;
@@ -332,8 +326,8 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int c = 0; c < 64; ++c)
                     if (g * 64 + c > row) sv[c] = -INFINITY;
             }
-            float gm = gm_pre;
-            if (!have_pre) {
+            float gm;
+            {
                 float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]);
 #pragma unroll
                 for (int c = 4; c < 64; c += 4) {
@@ -341,11 +335,9 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     m1 = dm::fmax3(m1, sv[c + 2], sv[c + 3]);
                 }
                 gm = fmaxf(m0, m1) * dsc;
-                s.gmax[b][g][row] = gm;
-                dm::mbar_arrive_warp(&s.bar_gm[b][warp & 3]);
             }
-            // the two key groups of a row quarter exchange their maxima (two warps, one barrier per quarter and tile parity)
-            dm::mbar_wait(&s.bar_gm[b][warp & 3], (t >> 1) & 1, wc);
+            s.gmax[b][g][row] = gm;
+            dm::named_bar_sync(1, kSoftmaxThreads);
             const float tile_max = fmaxf(s.gmax[b][0][row], s.gmax[b][1][row]);
             const float m_new = fmaxf(m_run, tile_max);
             const float m_cur = (m_new == -INFINITY) ? 0.f : m_new;
@@ -360,7 +352,8 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             float part0 = 0.f, part1 = 0.f;
             uint32_t codes[16];
             const float nms = -ms, cl = __fmul_rn(dsc, dm::kLog2e);
-            auto exp4 = [&](int c) {
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
                 float x0, x1, x2, x3;
                 dm::fma2(x0, x1, sv[c], sv[c + 1], cl, nms, nms);
                 dm::fma2(x2, x3, sv[c + 2], sv[c + 3], cl, nms, nms);
@@ -368,38 +361,7 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 dm::add2(part0, part1, p0, p1);
                 dm::add2(part0, part1, p2, p3);
                 codes[c >> 2] = dm::cvt_e4m3x4(p0, p1, p2, p3);
-            };
-#pragma unroll
-            for (int c = 0; c < 48; c += 4) exp4(c);
-            bool pre = false;
-            if (it + 1 < n_tiles)
-                pre = __all_sync(0xffffffffu, dm::mbar_test(&s.bar_s_full[b ^ 1], ((t + 1) >> 1) & 1));
-            if (pre) {
-                dm::tc_fence_after();
-                const uint32_t nxt = dm::tmem_addr(tmem + (b ^ 1) * 128, lane_base, g * 64);
-                float nx[16];
-                float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {                  // 16 columns at a time, each under four exponentials
-                    dm::tmem_ld16(nxt + 16 * h, reinterpret_cast<uint32_t*>(nx));
-                    exp4(48 + 4 * h);
-                    dm::tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 16; c += 4) {
-                        m0 = dm::fmax3(m0, nx[c], nx[c + 1]);
-                        m1 = dm::fmax3(m1, nx[c + 2], nx[c + 3]);
-                    }
-                }
-                gm_pre = fmaxf(m0, m1) * fmaxf(q8sc * ks_n, 1.2e-38f);
-                s.gmax[b ^ 1][g][row] = gm_pre;
-                dm::mbar_arrive_warp(&s.bar_gm[b ^ 1][warp & 3]);
-            } else {
-                exp4(48);
-                exp4(52);
-                exp4(56);
-                exp4(60);
             }
-            have_pre = pre;
             const float part = part0 + part1;
             l_part = fmaf(l_part, alpha, sigma * part);
             // the codes go back into tensor memory, over the first 16 columns of this thread's own 64 scores (all read by

@@ -94,28 +94,34 @@ __device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16
                                             const float* __restrict__ km, uint8_t* __restrict__ codes, float* __restrict__ scales,
                                             float* __restrict__ delta, int heads, int N, float sm) {
     constexpr int BLK = (MODE == 1 || MODE == 2) ? (D == 128 ? 64 : 32) : (D == 128 ? 128 : 64);
-    constexpr int E = D / 32;             // elements per lane
-    constexpr int RPW = BLK / 8;          // rows per warp
+    // A lane takes 16 bytes of a row where it can (half a warp per 256-byte row at head_dim 128, two rows per step): half
+    // the loads, stores and address arithmetic per element.  The stale-delta mode keeps four elements per lane, because
+    // its row sum is defined as per-lane partial sums of D / 32 elements under a butterfly over 32 lanes.
+    constexpr int E = (D == 128 && MODE != 4) ? 8 : D / 32;   // elements per lane
+    constexpr int LPR = D / E;            // lanes per row
+    constexpr int RW = 32 / LPR;          // rows per warp and step
+    constexpr int RPW = BLK / (8 * RW);   // steps per warp
     // Q, V and dO: the block maximum is a maximum of bf16 magnitudes (Q's multiply by a positive constant is monotone, so
     // it commutes with the maximum), which orders like their bit patterns: two elements per instruction, on the raw pairs.
     // K subtracts a per-column mean first and takes the float route.
     constexpr bool kPackedMax = MODE != 1;
     const int b = bh / heads, h = bh % heads;
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    const int col = (l % LPR) * E, sub = l / LPR;       // this lane's columns and its row within a step
     __shared__ float s_amax[8];
     __shared__ uint32_t s_bits[8];
 
     float kmv[E];
     if (MODE == 1) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) kmv[e] = km[(int64_t)bh * D + l * E + e];
+        for (int e = 0; e < E; ++e) kmv[e] = km[(int64_t)bh * D + col + e];
     }
     // the block stays in registers as raw bf16 pairs between the maximum and the codes
     uint32_t u[RPW][E / 2];
-    const __nv_bfloat16* xbase = x + b * sb + h * sh + l * E;
+    const __nv_bfloat16* xbase = x + b * sb + h * sh + col;
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
-        const int row = blk * BLK + r * 8 + w;
+        const int row = blk * BLK + (r * 8 + w) * RW + sub;
         const __nv_bfloat16* p = xbase + (int64_t)row * sn;
         if (E == 4) {
             uint2 t = *reinterpret_cast<const uint2*>(p);
@@ -170,7 +176,7 @@ __device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16
     const float s = (MODE >= 3) ? __fmul_rn(base, __fdiv_rn(1.0f, kE4M3Max)) : __fdiv_rn(base, kE4M3Max);
     if (threadIdx.x == 0) scales[(int64_t)bh * (N / BLK) + blk] = s;
 
-    uint8_t* cbase = codes + ((int64_t)bh * N) * D + l * E;
+    uint8_t* cbase = codes + ((int64_t)bh * N) * D + col;
     const float rcp = __frcp_rn(s);
     // kFinite: all elements finite and the scale inside the reciprocal's range.  Then the quotient is finite, so the
     // conversion's own saturation is the clamp, and its sign is the element's: the sign bits are copied from the bf16
@@ -179,7 +185,7 @@ __device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16
         constexpr bool kExactRcp = decltype(exact_rcp)::value, kFinite = decltype(all_finite)::value;
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
-            const int row = blk * BLK + r * 8 + w;
+            const int row = blk * BLK + (r * 8 + w) * RW + sub;
             uint32_t c4[E / 4];
 #pragma unroll
             for (int g = 0; g < E / 4; ++g) {
@@ -208,7 +214,7 @@ __device__ __forceinline__ void quant_block(int blk, int bh, const __nv_bfloat16
             }
             if (MODE == 4) {
                 // stale delta from the RAW dO and the bf16 O
-                const __nv_bfloat16* po = o + b * ob + h * oh + (int64_t)row * on + l * E;
+                const __nv_bfloat16* po = o + b * ob + h * oh + (int64_t)row * on + col;
                 uint32_t uo[E / 2];
                 if (E == 4) {
                     uint2 t = *reinterpret_cast<const uint2*>(po);
