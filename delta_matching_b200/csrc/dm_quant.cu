@@ -1,6 +1,7 @@
 // Producers: per-head K mean, block quantizers bf16 -> e4m3 codes + fp32 scales for Q, K, V, dO (with the optional
-// stale delta), and the GQA fold of per-query-head gradients.  All HBM-bound: one warp owns one row (256 or 512
-// contiguous bytes), loads are 8/16 bytes per lane, code stores 4/8 bytes per lane, block amax by warp shuffles.
+// stale delta), and the GQA fold of per-query-head gradients.  All HBM-bound: a warp owns one 512-byte row or two
+// 256-byte rows per step (16-byte loads, 8-byte code stores per lane; 8 / 4 bytes in the stale-delta mode at head_dim
+// 128), the block maximum is a warp reduction plus eight values in shared memory.
 //
 // Bit-exactness contract (checked against the CPU oracle, which is pinned to the reference's Triton kernels):
 //   * every arithmetic step is an explicitly rounded IEEE operation (__fmul_rn, __fsub_rn, __fdiv_rn, __fadd_rn), so
@@ -11,7 +12,8 @@
 //     formed from the block's correctly rounded reciprocal r = RN(1 / scale): q0 = RN(x r), then twice
 //     q <- RN(q + RN(x - q scale) r).  The residual is exact (FMA); the first correction leaves q within one ulp of
 //     x / scale, and a correction of a faithful quotient with a correctly rounded reciprocal rounds correctly
-//     (Markstein), so the result carries the bits of the division; copysign restores the sign of a zero quotient.  That
+//     (Markstein), so the result carries the bits of the division; the sign of a zero quotient is restored from the
+//     element (copysign, or in all-finite Q / V / dO blocks the sign bits copied into the four codes at once).  That
 //     holds while no intermediate leaves the normal range: blocks whose scale is outside [2^-60, 2^60] (all-tiny,
 //     huge or non-finite data) take the plain division instead, a branch that is uniform over the block;
 //   * K mean = (((0 + s_0) + s_1) + ...) / N with s_j the sum of the 64 rows of chunk j in ascending row order.
