@@ -58,7 +58,21 @@ struct WaitCtx {
     volatile int* abort_flag;   // shared memory
     int* status;                // global memory, one word per device (dm_device_status reads and clears it)
 };
+// One look at the barrier without suspending.  On a phase that has already completed this answers in about 60 clocks
+// where try_wait takes about 160, so every wait starts with it.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t limit) {
+    if (mbar_test(bar, parity)) return true;
     for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try(bar, parity)) return true;
         if ((it & 63u) == 63u && *ctx.abort_flag) return false;
