@@ -4,7 +4,7 @@
 //
 // One CTA = 128 query rows of one (batch, head); 256 threads.  A code row is 256 bytes = two 128-byte swizzled sub-tiles
 // (d 0..127 and d 128..255), so S = Q K^T is 8 tcgen05.mma K steps.  Thread (row, warpgroup g) owns key groups 2g and
-// 2g + 1 of the tile (S is read from tensor memory twice -- maxima, then codes -- because the registers hold O) and the
+// 2g + 1 of the tile (its 64 scores stay in registers from the maxima to the codes, beside the 128 columns of O) and the
 // d columns [128 g, 128 g + 128) of O.  Per group: D_grp = C_grp V_grp as two M128 N128 K32 MMAs (one per d half) into a
 // zero-initialised 256-column temporary, then O += D_grp * w_grp.  The four groups of a tile go through that one temporary
 // in turn.  Every mbarrier wait is bounded.
@@ -114,34 +114,52 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
     for (int i = 0; i < 128; ++i) o_acc[i] = 0.f;
     int d_phase = 0;
+    // the K / V scales of a tile are read one tile ahead: read at the tile's top they are two exposed global loads
+    const float* ksb = p.k8s + (int64_t)hc.bhk * (p.N / 32) + 2 * g;
+    const float* vsb = p.v8s + (int64_t)hc.bhk * (p.N / 32) + 2 * g;
+    float2 ks_n = *reinterpret_cast<const float2*>(ksb + 4 * (n_tiles - 1));
+    float2 vs_n = *reinterpret_cast<const float2*>(vsb + 4 * (n_tiles - 1));
 
     for (int it = 0; it < n_tiles; ++it) {
         const int j = n_tiles - 1 - it, st = it & 1;
-        const float* ksp = p.k8s + (int64_t)hc.bhk * (p.N / 32) + 4 * j + 2 * g;
-        const float* vsp = p.v8s + (int64_t)hc.bhk * (p.N / 32) + 4 * j + 2 * g;
-        const float dsc[2] = {q8sc * ksp[0], q8sc * ksp[1]};
-        const float vs[2] = {vsp[0], vsp[1]};
+        const float dsc[2] = {q8sc * ks_n.x, q8sc * ks_n.y};
+        const float vs[2] = {vs_n.x, vs_n.y};
+        if (it + 1 < n_tiles) {
+            ks_n = *reinterpret_cast<const float2*>(ksb + 4 * (j - 1));
+            vs_n = *reinterpret_cast<const float2*>(vsb + 4 * (j - 1));
+        }
         const bool diag = p.causal && j == I;
 
         dm::mbar_wait(&s.bar_s, it & 1, wc);
         dm::tc_fence_after();
         // ---- pass A: maxima of this thread's two 32-key groups (true units)
         float gm[2];
+        float s2[2][32];                                   // this thread's 64 scores, kept through both passes
+        dm::tmem_ld32(dm::tmem_addr(t_s, lane_base, g * 64), reinterpret_cast<uint32_t*>(s2[0]));
+        dm::tmem_ld32(dm::tmem_addr(t_s, lane_base, g * 64 + 32), reinterpret_cast<uint32_t*>(s2[1]));
+        dm::tmem_ld_wait();
 #pragma unroll
         for (int gg = 0; gg < 2; ++gg) {
-            float sv[32];
-            dm::tmem_ld32(dm::tmem_addr(t_s, lane_base, g * 64 + gg * 32), reinterpret_cast<uint32_t*>(sv));
-            dm::tmem_ld_wait();
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            float* sv = s2[gg];
+            if (diag) {                                    // the diagonal tile only: keys above the row never win the maximum
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const bool masked = diag && (g * 64 + gg * 32 + c > row);
-                mx[c & 3] = masked ? mx[c & 3] : fmaxf(mx[c & 3], sv[c]);
+                for (int c = 0; c < 32; ++c)
+                    if (g * 64 + gg * 32 + c > row) sv[c] = -INFINITY;
+            }
+            float mx[4] = {fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]), fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7])};
+#pragma unroll
+            for (int c = 8; c < 32; c += 8) {
+                mx[0] = dm::fmax3(mx[0], sv[c], sv[c + 1]);
+                mx[1] = dm::fmax3(mx[1], sv[c + 2], sv[c + 3]);
+                mx[2] = dm::fmax3(mx[2], sv[c + 4], sv[c + 5]);
+                mx[3] = dm::fmax3(mx[3], sv[c + 6], sv[c + 7]);
             }
             gm[gg] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * dsc[gg];
             s.gmax[2 * g + gg][row] = gm[gg];
         }
         __syncthreads();
+        // every thread holds its scores: S of the next tile may overwrite the buffer, under pass B and the products
+        if (tid == 0 && it + 1 < n_tiles) issue_s(it + 1);
         const float tile_max = fmaxf(fmaxf(s.gmax[0][row], s.gmax[1][row]), fmaxf(s.gmax[2][row], s.gmax[3][row]));
         const float m_new = fmaxf(m_run, tile_max);
         const float m_cur = (m_new == -INFINITY) ? 0.f : m_new;
@@ -154,22 +172,19 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int gg = 0; gg < 2; ++gg) {
             const float ms = fmaxf(gm[gg] * dm::kLog2e, ml2 - dm::kPhatFloorB) - dm::kLog2_448;
             const float dl2 = dsc[gg] * dm::kLog2e;
-            float sv[32];
-            dm::tmem_ld32(dm::tmem_addr(t_s, lane_base, g * 64 + gg * 32), reinterpret_cast<uint32_t*>(sv));
-            dm::tmem_ld_wait();
+            float* sv = s2[gg];                            // still in registers, masked
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t codes[8];
+            const float nms = -ms;
 #pragma unroll
             for (int c = 0; c < 32; c += 4) {
-                float pv[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float x = sv[c + e];
-                    if (diag && (g * 64 + gg * 32 + c + e > row)) x = -INFINITY;
-                    pv[e] = dm::ex2(fmaf(x, dl2, -ms));
-                    acc[e] += pv[e];
-                }
-                codes[c >> 2] = dm::cvt_e4m3x4(pv[0], pv[1], pv[2], pv[3]);
+                float x0, x1, x2, x3;
+                dm::fma2(x0, x1, sv[c], sv[c + 1], dl2, nms, nms);
+                dm::fma2(x2, x3, sv[c + 2], sv[c + 3], dl2, nms, nms);
+                const float p0 = dm::ex2(x0), p1 = dm::ex2(x1), p2 = dm::ex2(x2), p3 = dm::ex2(x3);
+                dm::add2(acc[0], acc[1], p0, p1);
+                dm::add2(acc[2], acc[3], p2, p3);
+                codes[c >> 2] = dm::cvt_e4m3x4(p0, p1, p2, p3);
             }
             const float sigma = dm::ex2(ms - ml2);
             lacc = fmaf(sigma, (acc[0] + acc[1]) + (acc[2] + acc[3]), lacc);
@@ -203,21 +218,25 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ++d_phase;
             dm::tc_fence_after();
             const float w = s.wgt[grp][row];
+            // 32 columns are added while the next 32 are on their way from tensor memory
+            const uint32_t src = dm::tmem_addr(t_d, lane_base, g * 128);
+            uint32_t sa[32], sb[32];
+            dm::tmem_ld32(src, sa);
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-                float dv[32];
-                dm::tmem_ld32(dm::tmem_addr(t_d, lane_base, g * 128 + h * 32), reinterpret_cast<uint32_t*>(dv));
+                uint32_t* cur = (h & 1) ? sb : sa;
+                uint32_t* nxt = (h & 1) ? sa : sb;
                 dm::tmem_ld_wait();
+                if (h < 3) dm::tmem_ld32(src + 32 * (h + 1), nxt);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[h * 32 + i] = fmaf(dv[i], w, o_acc[h * 32 + i]);
+                for (int i = 0; i < 32; i += 2)
+                    dm::fma2(o_acc[h * 32 + i], o_acc[h * 32 + i + 1], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]), w,
+                             o_acc[h * 32 + i], o_acc[h * 32 + i + 1]);
             }
             dm::tc_fence_before();
             __syncthreads();                               // the product buffer may be overwritten
         }
-        if (tid == 0) {
-            if (it + 1 < n_tiles) issue_s(it + 1);
-            if (it + 2 < n_tiles) load_kv(it + 2);
-        }
+        if (tid == 0 && it + 2 < n_tiles) load_kv(it + 2);
     }
 
     // ---- epilogue
