@@ -94,6 +94,11 @@ __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// The producer side of a named barrier: counts this warp's threads in and goes on.  `nthreads` is the total of arriving
+// and synchronising threads; the arriving side must not get a whole round ahead of the synchronising side.
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // Register re-allocation between warpgroups (all 128 threads of a warpgroup execute it): the issuer warpgroup gives
 // registers back, the compute warpgroups take them.  Counts are multiples of 8.
