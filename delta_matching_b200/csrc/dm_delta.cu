@@ -463,13 +463,13 @@ int launch(const void* q8, const void* k8, const void* v8, const void* do8, cons
     if ((rc = dmh::make_tmap_u8(&tk, k8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::make_tmap_u8(&tv, v8, kD, (uint64_t)sh.B * sh.Hk * sh.N, 128, err, errlen))) return rc;
     if ((rc = dmh::prepare_delta(err, errlen))) return rc;
-    // head_dim 128, production: the persistent kernel once every CTA has a long walk (at least 64 key tiles each: measured, it
-    // wins from there on); the one-item-per-CTA kernel below stays for small problems, the debug row sums and head_dim 256
+    // head_dim 128, production: the persistent kernel once every CTA has a walk of at least 24 key tiles (measured: it wins at
+    // 29 tiles per CTA, 0.041 against 0.044 ms, and by more on longer walks); the one-item-per-CTA kernel below stays for small problems, the debug row sums and head_dim 256
     const int64_t items = (int64_t)sh.B * p.hcount * (p.rm.nq / 128);
     const int64_t tiles = items * (sh.causal ? (sh.N / 128 + 1) / 2 : sh.N / 128);      // about: exact for the identity row map
     int sms = 0;
     if ((rc = dmh::sm_count(&sms, err, errlen))) return rc;
-    if (!kDebug && kD == 128 && items >= 2 * (int64_t)sms && tiles >= 64 * (int64_t)sms) {
+    if (!kDebug && kD == 128 && items >= 2 * (int64_t)sms && tiles >= 24 * (int64_t)sms) {
         const DeltaDivs fd{dm::make_fastdiv(sh.B * p.hcount), dm::make_fastdiv(p.hcount), dm::make_fastdiv(sh.H / sh.Hk)};
         delta_roles_kernel<<<sms, kDzThreads, (int)sizeof(DeltaRolesSmem) + 1024, static_cast<cudaStream_t>(stream)>>>(tq, td, tk, tv, p, fd);
         DM_CUDA(cudaGetLastError());
