@@ -193,7 +193,8 @@ def run_reference_arm(args, cfg, rank, world):
     tf = statistics.mean(v[0] for v in vals)
     ms = statistics.mean(v[1] for v in vals) * 1e3
     line = {"impl": "reference", "metric": "fp8_attn_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak" if world == 1 or args.scaling == "weak" else "strong",      # the key of the GPU arm's line
             "vs_baseline": None, "dtype": "e4m3", "data": "synthetic",
             "config": workload_config(args.config, cfg),
             "parallelism": "host (CPU oracle: PyTorch restatement of the reference numerics; the reference's own kernels are "
