@@ -32,6 +32,7 @@ constexpr int kThreads128 = kFoldThreads + 64;
 struct Bwd2Smem {
     alignas(1024) uint8_t a[kRing][kTile];   // dS' tile [key][row]
     alignas(1024) uint8_t b[kRing][kTile];   // K8 tile [key][d]
+    alignas(16) uint8_t stg[128 * 256];       // an item's bf16 dQ rows on their way out (16-byte chunks XOR-swizzled by the row)
     uint64_t bar_ld[kRing], bar_free[kRing], bar_acc[kAcc], bar_acc_free[kAcc];
     uint32_t tmem_base;
     int abort_flag;
@@ -163,11 +164,13 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
             float dq[64];
 #pragma unroll
             for (int i = 0; i < 64; ++i) dq[i] = 0.f;
-            float psi_nx = psi_row[0];
+            // psi is read two tiles ahead: a new 32-byte sector of the row comes from DRAM every eighth tile
+            float psi_n1 = psi_row[0], psi_n2 = w.n_it > 1 ? psi_row[1] : 0.f;
             for (int it = 0; it < w.n_it; ++it) {
                 const int t = gt + it, b = t % kAcc;
-                const float psi_cur = psi_nx;
-                if (it + 1 < w.n_it) psi_nx = psi_row[it + 1];
+                const float psi_cur = psi_n1;
+                psi_n1 = psi_n2;
+                if (it + 2 < w.n_it) psi_n2 = psi_row[it + 2];
                 const bool take = (psi_cur != 0.f) && !(psi_cur < psi_max * 1e-8f);
                 dm::mbar_wait(&s.bar_acc[b], (t / kAcc) & 1, wc);
                 dm::tc_fence_after();
@@ -187,8 +190,8 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
                 dm::mbar_arrive_warp(&s.bar_acc_free[b]);
             }
             gt += w.n_it;
-            const int n_glob = w.rb * 128 + row;
-            __nv_bfloat16* op = p.dq + (((int64_t)w.hc.b * p.rm.nq + n_glob) * p.H + w.hc.h) * 128 + g * 64;
+            // The bf16 rows leave through shared memory: a thread holds half a row, so stored directly every 16-byte store
+            // instruction would touch 32 different rows; from the staging tile each instruction writes two whole 256-byte rows.
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w4[4];
@@ -197,8 +200,21 @@ bwd2_d128_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
                     __nv_bfloat162 tt = __floats2bfloat162_rn(dq[8 * c + 2 * e] * p.final_scale, dq[8 * c + 2 * e + 1] * p.final_scale);
                     w4[e] = *reinterpret_cast<uint32_t*>(&tt);
                 }
-                reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                *reinterpret_cast<uint4*>(s.stg + row * 256 + (((g * 8 + c) ^ (row & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
+            dm::named_bar_sync(1, kFoldThreads);
+            {
+                uint8_t* obase = reinterpret_cast<uint8_t*>(p.dq + (((int64_t)w.hc.b * p.rm.nq + w.rb * 128) * p.H + w.hc.h) * 128);
+                const int64_t row_bytes = (int64_t)p.H * 128 * 2;
+                const int j = lane & 15;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = 2 * (warp * 8 + i) + (lane >> 4);
+                    const uint4 val = *reinterpret_cast<const uint4*>(s.stg + rr * 256 + ((j ^ (rr & 7)) << 4));
+                    *reinterpret_cast<uint4*>(obase + rr * row_bytes + (j << 4)) = val;
+                }
+            }
+            dm::named_bar_sync(1, kFoldThreads);           // the staging tile may take the next item's rows
         }
     }
     dm::tc_fence_before();
