@@ -39,6 +39,7 @@ struct FwdSmem {
     float alpha[kRing][128];
     float lsum[4][2][128];            // [work item % 4][key group][row]: with one-tile items the softmax warps can be three
                                       // items ahead of the fold warps
+    alignas(16) uint8_t stg[4][32 * 256];   // per fold warp: its 32 bf16 O rows on their way out (16-byte chunks XOR-swizzled by the row)
     uint64_t bar_q[2], bar_q_free[2], bar_kv[kStages], bar_kv_free[kStages], bar_s_full[2], bar_s_free[2], bar_codes[2],
         bar_d_full[2], bar_d_free, bar_l[4];
     uint32_t tmem_base;
@@ -258,8 +259,10 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float l = s.lsum[r & 3][0][row] + s.lsum[r & 3][1][row];
             const bool dead = (l == 0.f) || (l != l);
             const float inv = dead ? 0.f : 1.0f / l;
-            const int n_glob = w.li * 128 + row;          // row inside the (local) Q-side tensors
-            __nv_bfloat16* op = p.o + (((int64_t)w.hc.b * p.rm.nq + n_glob) * p.H + w.hc.h) * 128;
+            // The bf16 rows leave through shared memory: a thread holds a whole row, so stored directly every 16-byte store
+            // instruction would touch 32 different rows; from the warp's staging slice each instruction writes two whole 256-byte
+            // rows.  A warp's 32 rows are its own, so the hand-over needs no more than the warp.
+            uint8_t* stg = s.stg[warp & 3];
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
                 uint32_t w4[4];
@@ -268,8 +271,22 @@ fwd_d128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     __nv_bfloat162 tt = __floats2bfloat162_rn(o_acc[8 * c + 2 * e] * inv, o_acc[8 * c + 2 * e + 1] * inv);
                     w4[e] = *reinterpret_cast<uint32_t*>(&tt);
                 }
-                reinterpret_cast<uint4*>(op)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((c ^ (lane & 15)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
+            __syncwarp();
+            {
+                const int row0 = w.li * 128 + (warp & 3) * 32;          // first of the warp's rows inside the (local) Q-side tensors
+                uint8_t* obase = reinterpret_cast<uint8_t*>(p.o + (((int64_t)w.hc.b * p.rm.nq + row0) * p.H + w.hc.h) * 128);
+                const int64_t row_bytes = (int64_t)p.H * 128 * 2;
+                const int j = lane & 15;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int rr = 2 * i + (lane >> 4);
+                    const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((j ^ (rr & 15)) << 4));
+                    *reinterpret_cast<uint4*>(obase + rr * row_bytes + (j << 4)) = val;
+                }
+            }
+            __syncwarp();                                  // the slice may take the next item's rows
         }
     } else {
         // =============================================================== softmax warps
