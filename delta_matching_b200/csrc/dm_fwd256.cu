@@ -201,40 +201,48 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         dm::tc_fence_before();
         __syncthreads();                                   // S consumed, P codes and weights visible
 
-        // ---- the four groups through the one product buffer
+        // ---- the four groups through the one product buffer.  A group's last two 32-column pieces are held in registers
+        // while thread 0 issues the next group's products, so those form under the additions instead of after them.
+        auto issue_pv = [&](int grp) {   // thread 0 only
+            dm::tc_fence_after();
+            const uint64_t pd = dm::smem_desc_sw128(dm::smem_u32(s.p)) + 2 * grp;      // 32 bytes of keys per group
+#pragma unroll
+            for (int dh = 0; dh < 2; ++dh) {
+                const uint64_t vd = dm::smem_desc_sw128(dm::smem_u32(s.v[st][dh])) + 256 * grp;   // 32 key rows = 4096 bytes
+                dm::umma_e4m3(t_d + 128 * dh, pd, vd, idesc_pv, 0);
+            }
+            dm::umma_commit(&s.bar_d);
+        };
+        if (tid == 0) issue_pv(0);
 #pragma unroll 1
         for (int grp = 0; grp < 4; ++grp) {
-            if (tid == 0) {
-                dm::tc_fence_after();
-                const uint64_t pd = dm::smem_desc_sw128(dm::smem_u32(s.p)) + 2 * grp;      // 32 bytes of keys per group
-#pragma unroll
-                for (int dh = 0; dh < 2; ++dh) {
-                    const uint64_t vd = dm::smem_desc_sw128(dm::smem_u32(s.v[st][dh])) + 256 * grp;   // 32 key rows = 4096 bytes
-                    dm::umma_e4m3(t_d + 128 * dh, pd, vd, idesc_pv, 0);
-                }
-                dm::umma_commit(&s.bar_d);
-            }
             dm::mbar_wait(&s.bar_d, d_phase & 1, wc);
             ++d_phase;
             dm::tc_fence_after();
             const float w = s.wgt[grp][row];
-            // 32 columns are added while the next 32 are on their way from tensor memory
             const uint32_t src = dm::tmem_addr(t_d, lane_base, g * 128);
             uint32_t sa[32], sb[32];
-            dm::tmem_ld32(src, sa);
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-                uint32_t* cur = (h & 1) ? sb : sa;
-                uint32_t* nxt = (h & 1) ? sa : sb;
-                dm::tmem_ld_wait();
-                if (h < 3) dm::tmem_ld32(src + 32 * (h + 1), nxt);
+            auto add32 = [&](int h, const uint32_t* piece) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 2)
-                    dm::fma2(o_acc[h * 32 + i], o_acc[h * 32 + i + 1], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]), w,
+                    dm::fma2(o_acc[h * 32 + i], o_acc[h * 32 + i + 1], __uint_as_float(piece[i]), __uint_as_float(piece[i + 1]), w,
                              o_acc[h * 32 + i], o_acc[h * 32 + i + 1]);
-            }
+            };
+            dm::tmem_ld32(src, sa);
+            dm::tmem_ld_wait();
+            dm::tmem_ld32(src + 32, sb);
+            add32(0, sa);
+            dm::tmem_ld_wait();
+            dm::tmem_ld32(src + 64, sa);
+            add32(1, sb);
+            dm::tmem_ld_wait();
+            dm::tmem_ld32(src + 96, sb);
+            dm::tmem_ld_wait();
             dm::tc_fence_before();
-            __syncthreads();                               // the product buffer may be overwritten
+            __syncthreads();                               // every thread holds its last two pieces: the buffer is free
+            if (tid == 0 && grp < 3) issue_pv(grp + 1);
+            add32(2, sa);
+            add32(3, sb);
         }
         if (tid == 0 && it + 2 < n_tiles) load_kv(it + 2);
     }
