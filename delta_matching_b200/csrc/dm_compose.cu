@@ -33,9 +33,8 @@ extern "C" int dm_attn_backward(const void* dO, DmStrides dos, const void* o, Dm
     if ((rc = dm_bwd_fp8_pass1(q8, k8, v8, do8, q8s, k8s, v8s, do8s, lse, delta, s, 0, s.H, dkh, dvh, ds8_ws, psi_ws, stream, err, errlen)))
         return rc;
     if ((rc = dm_bwd_fp8_pass2(ds8_ws, psi_ws, k8, s, 0, s.H, dq, stream, err, errlen))) return rc;
-    if (gqa) {
-        if ((rc = dm_gqa_fold(dkh, s.B, s.N, s.H, s.Hk, s.D, dk, stream, err, errlen))) return rc;
-        if ((rc = dm_gqa_fold(dvh, s.B, s.N, s.H, s.Hk, s.D, dv, stream, err, errlen))) return rc;
+    if (gqa) {      // dK and dV in one launch
+        if ((rc = dmh::launch_gqa_fold(dkh, dk, dvh, dv, s.B, s.N, s.H, s.Hk, s.D, stream, err, errlen))) return rc;
     }
     return DM_OK;
 }

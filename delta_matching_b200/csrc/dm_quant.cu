@@ -281,8 +281,11 @@ __global__ void __launch_bounds__(256) prologue_kernel(const PrologueArgs a) {
 }
 
 // ---- GQA fold -------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) gqa_fold_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int64_t total_vec, int H,
-                                                       int Hk, int D) {
+// blockIdx.y picks one of up to two (input, output) pairs of the same shape: dK and dV of a backward fold in one launch.
+__global__ void __launch_bounds__(256) gqa_fold_kernel(const uint4* __restrict__ x0, uint4* __restrict__ out0, const uint4* __restrict__ x1,
+                                                       uint4* __restrict__ out1, int64_t total_vec, int H, int Hk, int D) {
+    const uint4* __restrict__ x = blockIdx.y ? x1 : x0;
+    uint4* __restrict__ out = blockIdx.y ? out1 : out0;
     const int vpr = D / 8;                                   // 16-byte vectors per head row
     const int rep = H / Hk;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
@@ -580,20 +583,32 @@ extern "C" int dm_quant_do(const void* dO, DmStrides dos, const void* o, DmStrid
     return DM_OK;
 }
 
-extern "C" int dm_gqa_fold(const void* x, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, void* out, void* stream, char* err,
-                           size_t errlen) {
+namespace dmh {
+// One launch for one pair (x1 == nullptr) or two pairs of the same shape.
+int launch_gqa_fold(const void* x0, void* out0, const void* x1, void* out1, int B, int N, int H, int Hk, int D, void* stream, char* err,
+                    size_t errlen) {
     DM_REQUIRE(B > 0 && N > 0 && H > 0 && Hk > 0 && H % Hk == 0, DM_ERR_ARG, "nheads (%d) must be a positive multiple of nheads_k (%d)", H, Hk);
     DM_REQUIRE(D % 8 == 0, DM_ERR_ARG, "head_dim must be a multiple of 8");
     int rc;
-    if ((rc = dmh::check_device_ptr(x, "x", err, errlen))) return rc;
-    if ((rc = dmh::check_device_ptr(out, "out", err, errlen))) return rc;
-    DM_REQUIRE(dmh::aligned16(x) && dmh::aligned16(out), DM_ERR_ARG, "x / out must be 16-byte aligned");
+    const void* ptrs[] = {x0, out0, x1, out1};
+    const char* names[] = {"x", "out", "x (second pair)", "out (second pair)"};
+    for (int i = 0; i < (x1 ? 4 : 2); ++i) {
+        if ((rc = check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
+        DM_REQUIRE(aligned16(ptrs[i]), DM_ERR_ARG, "x / out must be 16-byte aligned");
+    }
     const int64_t total = (int64_t)B * N * Hk * (D / 8);
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    gqa_fold_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(x), static_cast<uint4*>(out), total, H, Hk, D);
+    gqa_fold_kernel<<<dim3(blocks, x1 ? 2 : 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x0), static_cast<uint4*>(out0), static_cast<const uint4*>(x1), static_cast<uint4*>(out1), total, H, Hk, D);
     DM_CUDA(cudaGetLastError());
     return DM_OK;
+}
+}  // namespace dmh
+
+extern "C" int dm_gqa_fold(const void* x, int32_t B, int32_t N, int32_t H, int32_t Hk, int32_t D, void* out, void* stream, char* err,
+                           size_t errlen) {
+    return dmh::launch_gqa_fold(x, out, nullptr, nullptr, B, N, H, Hk, D, stream, err, errlen);
 }
 
 // ---- K mean without any allocation ------------------------------------------------------------------------------------
