@@ -8,10 +8,10 @@ extern "C" int dm_attn_forward(const void* q, DmStrides qs, const void* k, DmStr
                                void* q8, float* q8s, void* k8, float* k8s, void* v8, float* v8s, float* km, float* km_partials,
                                void* o, float* lse, void* stream, char* err, size_t errlen) {
     int rc;
-    // four launches: {K column sums, Q codes, V codes}, the fold of the sums into the K mean, K codes, attention
+    // three or four launches: {K column sums, Q codes, V codes}, the fold of the sums into the K mean and the K codes (one launch
+    // up to 8192 keys, two beyond), attention
     if ((rc = dm_quant_qv_kpartials(q, qs, k, ks, v, vs, s, q8, q8s, v8, v8s, km_partials, stream, err, errlen))) return rc;
-    if ((rc = dm_kmean_fold(km_partials, s.B, s.Hk, s.N, s.D, km, stream, err, errlen))) return rc;
-    if ((rc = dm_quant(1, k, ks, s.B, s.Hk, s.N, s.D, km, k8, k8s, stream, err, errlen))) return rc;
+    if ((rc = dmh::launch_kmean_fold_quant_k(k, ks, km_partials, s, km, k8, k8s, stream, err, errlen))) return rc;
     return dm_fwd_fp8(q8, k8, v8, q8s, k8s, v8s, s, 0, s.H, o, lse, stream, err, errlen);
 }
 

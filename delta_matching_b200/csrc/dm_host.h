@@ -75,6 +75,8 @@ int sm_count(int* sms, char* err, size_t errlen);
 // One-time set-up of each kernel family on the current device (also reached lazily from the entry points).
 int prepare_fwd(char* err, size_t errlen);
 int prepare_fwd256(char* err, size_t errlen);
+int launch_kmean_fold_quant_k(const void* k, DmStrides ks, const float* partials, DmShape s, float* km, void* k8, float* k8s, void* stream,
+                              char* err, size_t errlen);
 int launch_gqa_fold(const void* x0, void* out0, const void* x1, void* out1, int B, int N, int H, int Hk, int D, void* stream, char* err,
                     size_t errlen);
 int prepare_delta(char* err, size_t errlen);

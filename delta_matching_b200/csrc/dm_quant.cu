@@ -252,6 +252,27 @@ __global__ void __launch_bounds__(256) quant_kernel(const __nv_bfloat16* __restr
     quant_block<D, MODE>(blockIdx.x, blockIdx.y, x, sb, sn, sh, o, ob, on, oh, km, codes, scales, delta, heads, N, sm);
 }
 
+// The K quantizer with the K mean's fold in front of it, for short sequences: every block folds the head's chunk sums itself
+// (same order and division as kmean_fold_kernel, so the same bits; N / 64 additions per column, read from L2), which saves
+// the fold's launch; the first block of a head also writes the mean out.
+template <int D>
+__global__ void __launch_bounds__(256) quant_k_folded_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sn, int64_t sh,
+                                                             const float* __restrict__ partials, float* __restrict__ km_out,
+                                                             uint8_t* __restrict__ codes, float* __restrict__ scales, int heads, int N) {
+    __shared__ float s_km[D];
+    const int bh = blockIdx.y;
+    if (threadIdx.x < D) {
+        const float* p = partials + (int64_t)bh * (N / 64) * D + threadIdx.x;
+        float acc = 0.f;
+        for (int j = 0; j < N / 64; ++j) acc = __fadd_rn(acc, p[(int64_t)j * D]);
+        const float m = __fdiv_rn(acc, (float)N);
+        s_km[threadIdx.x] = m;
+        if (blockIdx.x == 0) km_out[(int64_t)bh * D + threadIdx.x] = m;
+    }
+    __syncthreads();
+    quant_block<D, 1>(blockIdx.x, bh, x, sb, sn, sh, nullptr, 0, 0, 0, s_km - (int64_t)bh * D, codes, scales, nullptr, heads, N, 0.f);
+}
+
 // The three producers of the forward that depend on nothing but the inputs, in one launch: K's per-chunk column sums
 // (first in the grid: the K quantizer waits for them through the fold), the Q quantizer and the V quantizer.  A block
 // does exactly what a block of the separate kernels does, so the results carry the same bits.
@@ -555,6 +576,29 @@ extern "C" int dm_quant(int32_t mode, const void* x, DmStrides xs, int32_t B, in
     DM_CUDA(cudaGetLastError());
     return DM_OK;
 }
+
+namespace dmh {
+// K mean from the chunk sums + K codes: one launch while the fold is short (N / 64 <= 128), else the fold and the quantizer.
+int launch_kmean_fold_quant_k(const void* k, DmStrides ks, const float* partials, DmShape s, float* km, void* k8, float* k8s, void* stream,
+                              char* err, size_t errlen) {
+    int rc;
+    if (s.N / 64 > 128 || s.D == 256) {
+        if ((rc = dm_kmean_fold(partials, s.B, s.Hk, s.N, s.D, km, stream, err, errlen))) return rc;
+        return dm_quant(1, k, ks, s.B, s.Hk, s.N, s.D, km, k8, k8s, stream, err, errlen);
+    }
+    if ((rc = check_geometry(s.B, s.Hk, s.N, s.D, err, errlen))) return rc;
+    const void* ptrs[] = {k, partials, km, k8, k8s};
+    const char* names[] = {"k", "partials", "km", "k8", "k8s"};
+    for (int i = 0; i < 5; ++i)
+        if ((rc = check_device_ptr(ptrs[i], names[i], err, errlen))) return rc;
+    if ((rc = check_strides(k, ks, s.D, "k", err, errlen))) return rc;
+    DM_REQUIRE(aligned16(k8), DM_ERR_ARG, "codes is not 16-byte aligned");
+    quant_k_folded_kernel<128><<<dim3(s.N / 64, s.B * s.Hk), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(k), ks.b, ks.n, ks.h, partials, km, static_cast<uint8_t*>(k8), k8s, s.Hk, s.N);
+    DM_CUDA(cudaGetLastError());
+    return DM_OK;
+}
+}  // namespace dmh
 
 extern "C" int dm_quant_do(const void* dO, DmStrides dos, const void* o, DmStrides os, int32_t B, int32_t H, int32_t N, int32_t D,
                            void* codes, float* scales, float* delta, void* stream, char* err, size_t errlen) {
